@@ -9,7 +9,11 @@
 // [K | V][kv head][slot][hd]; `planes` = 1: a page is [kv head][slot][hd] and a key is also its value.  Queries are
 // read from rows of `q_stride` elements (the packed output of a projection, or [T, H, hd] itself).  With `planes` = 1 the
 // value may be narrower than the key: `vd` <= hd says how many leading elements of a key are its value (a cache of latent
-// vectors with a positional part behind them); the output rows are [T, H, vd].
+// vectors with a positional part behind them); the output rows are [T, H, vd].  More generally with `planes` = 1 an entry
+// of a kv head is `ew` >= hd elements wide, its first hd elements are the key and the vd elements from `voff` on are the
+// value (ew = hd, voff = 0: the key's leading elements; ew = hd + vd, voff = hd: a key with its own value behind it, of
+// any size).  With a distance table `bias` [H, bias_len] (float) the score receives bias[h, min(p - j, bias_len - 1)] after
+// the scale: a learned bias per head and distance, whose last entry serves every larger distance.
 //
 // Formulas (reference kernels/paged_attention.cu:89-359 and model/model_architecture.cpp:134,147):
 //   query head h uses kv head h / (H / KV);  s_j = scale * q . k_j  for lo <= j <= p, others excluded;
@@ -29,7 +33,8 @@ paged_attention_general_kernel(T* __restrict__ out, const T* __restrict__ q, con
                                const int* __restrict__ block_tables, int table_width,
                                const int* __restrict__ seq_of_token, const int* __restrict__ positions,
                                int H, int KV, int hd, int vd, int page_size, int window, int keep_first, int planes, int q_stride,
-                               float scale, int num_pages, int* __restrict__ err) {
+                               float scale, int num_pages, int ew, int voff_in_entry, const float* __restrict__ bias, int bias_len,
+                               int* __restrict__ err) {
     pdl_trigger();
     pdl_wait();
     extern __shared__ int64_t smem64[];
@@ -68,12 +73,13 @@ paged_attention_general_kernel(T* __restrict__ out, const T* __restrict__ q, con
             if (page < 0 || page >= num_pages) {
                 atomicExch(err, 4);                     // a key this token must see has no page
             } else {
-                const int64_t koff = (((static_cast<int64_t>(page) * planes + 0) * KV + kvh) * page_size + j % page_size) * hd;
-                voff = (((static_cast<int64_t>(page) * planes + (planes - 1)) * KV + kvh) * page_size + j % page_size) * hd;
+                const int64_t koff = (((static_cast<int64_t>(page) * planes + 0) * KV + kvh) * page_size + j % page_size) * ew;
+                voff = (((static_cast<int64_t>(page) * planes + (planes - 1)) * KV + kvh) * page_size + j % page_size) * ew + voff_in_entry;
                 const T* kp = cache + koff;
                 float d = 0.f;
                 for (int e = 0; e < hd; ++e) d = fmaf(qs[e], to_float(kp[e]), d);
                 s = d * scale;
+                if (bias != nullptr) s += bias[static_cast<int64_t>(h) * bias_len + min(p - j, bias_len - 1)];
             }
         }
         const float tile_max = block_max(s, scratch);
@@ -113,25 +119,46 @@ paged_attention_general_kernel(T* __restrict__ out, const T* __restrict__ q, con
 
 using namespace cvb;
 
-extern "C" int cvb_paged_attention_general(void* out, const void* q, const void* cache, const int* block_tables,
-                                           int table_width, const int* seq_of_token, const int* positions, int T,
-                                           int H, int KV, int hd, int vd, int page_size, int window, int keep_first, int planes,
-                                           int q_stride, float scale, int num_pages, int dtype, int* err_flag,
-                                           cudaStream_t stream) {
+static int attention_general_launch(void* out, const void* q, const void* cache, const int* block_tables,
+                                    int table_width, const int* seq_of_token, const int* positions, int T,
+                                    int H, int KV, int hd, int vd, int page_size, int window, int keep_first, int planes,
+                                    int q_stride, float scale, int num_pages, int ew, int voff, const float* bias, int bias_len,
+                                    int dtype, int* err_flag, cudaStream_t stream) {
     if (T == 0) return CVB_OK;
     if (T < 0 || H <= 0 || KV <= 0 || hd <= 0 || page_size <= 0 || table_width <= 0 || num_pages <= 0)
         return CVB_E_SIZE;
-    if (hd > kAttnThreads * kMaxDimsPerThread) return CVB_E_SIZE;
+    if (hd > kAttnThreads * kMaxDimsPerThread || vd > kAttnThreads * kMaxDimsPerThread) return CVB_E_SIZE;
     if (H % KV || (planes != 1 && planes != 2) || keep_first < 0 || q_stride < H * hd) return CVB_E_SHAPE;
-    if (vd <= 0 || vd > hd || (planes == 2 && vd != hd)) return CVB_E_SHAPE;
+    if (vd <= 0 || ew < hd || voff < 0 || voff + vd > ew || (planes == 2 && (vd != hd || ew != hd || voff != 0))) return CVB_E_SHAPE;
+    if (bias != nullptr && bias_len <= 0) return CVB_E_SHAPE;
     if (H > 65535) return CVB_E_SIZE;
     dim3 grid(static_cast<unsigned>(T), static_cast<unsigned>(H));
     const size_t smem = kAttnThreads * sizeof(int64_t) + (static_cast<size_t>(hd) + kAttnThreads + 32) * sizeof(float);
 #define CALL(TY)                                                                                         \
     launch_kernel(paged_attention_general_kernel<TY>, dim3(grid), dim3(kAttnThreads), smem, stream,                             \
         (TY*)out, (const TY*)q, (const TY*)cache, block_tables, table_width, seq_of_token, positions, H, \
-        KV, hd, vd, page_size, window, keep_first, planes, q_stride, scale, num_pages, err_flag)
+        KV, hd, vd, page_size, window, keep_first, planes, q_stride, scale, num_pages, ew, voff, bias, bias_len, err_flag)
     CVB_DISPATCH_DTYPE(dtype, CALL);
 #undef CALL
     return launch_status();
+}
+
+extern "C" int cvb_paged_attention_general(void* out, const void* q, const void* cache, const int* block_tables,
+                                           int table_width, const int* seq_of_token, const int* positions, int T,
+                                           int H, int KV, int hd, int vd, int page_size, int window, int keep_first, int planes,
+                                           int q_stride, float scale, int num_pages, int dtype, int* err_flag,
+                                           cudaStream_t stream) {
+    if (vd <= 0 || vd > hd) return CVB_E_SHAPE;
+    return attention_general_launch(out, q, cache, block_tables, table_width, seq_of_token, positions, T, H, KV, hd, vd, page_size,
+                                    window, keep_first, planes, q_stride, scale, num_pages, hd, 0, nullptr, 0, dtype, err_flag, stream);
+}
+
+// Entries [key (hd) | value (vd)] per kv head (pages [page, kv head, slot, hd + vd]) and an optional distance table.
+extern "C" int cvb_paged_attention_entries(void* out, const void* q, const void* cache, const int* block_tables,
+                                           int table_width, const int* seq_of_token, const int* positions, int T,
+                                           int H, int KV, int hd, int vd, int page_size, int window, int q_stride, float scale,
+                                           int num_pages, const float* bias, int bias_len, int dtype, int* err_flag,
+                                           cudaStream_t stream) {
+    return attention_general_launch(out, q, cache, block_tables, table_width, seq_of_token, positions, T, H, KV, hd, vd, page_size,
+                                    window, 0, 1, q_stride, scale, num_pages, hd + vd, hd, bias, bias_len, dtype, err_flag, stream);
 }

@@ -42,6 +42,7 @@ LIBRARIES: Dict[str, List[str]] = {
     "moe": ["moe.cu"],
     "latent": ["latent.cu"],
     "recurrent": ["recurrent.cu"],
+    "sandwich": ["sandwich.cu"],
     # host code only (the cache manager and the scheduler); nvcc hands it to the host compiler
     "runtime": ["cache_runtime.cpp", "scheduler_runtime.cpp"],
 }

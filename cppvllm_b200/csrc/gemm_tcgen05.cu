@@ -35,7 +35,7 @@ constexpr int kBK = 64;                       // one 128-byte swizzle span of bf
 constexpr int kGemmThreads = 192;
 constexpr int kBoxBytes = 32 * 64 * 2;        // what a warp of the epilogue hands to one TMA store: 32 rows of 64 bf16
 
-enum GemmEpilogue { kPlain = 0, kSwiglu = 1, kAddResidual = 2 };
+enum GemmEpilogue { kPlain = 0, kSwiglu = 1, kAddResidual = 2, kRelu2 = 3 };   // kRelu2: C = relu(T(A B^T))^2
 
 struct GemmParams {
     __nv_bfloat16* out;       // [M, n_out]
@@ -218,6 +218,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                                 y0 = rnd<__nv_bfloat16>(__fdividef(g0, 1.f + __expf(-g0))) * u0;
                                 y1 = rnd<__nv_bfloat16>(__fdividef(g1, 1.f + __expf(-g1))) * u1;
                             }
+                            if constexpr (EPI == kRelu2) {
+                                y0 = fmaxf(rnd<__nv_bfloat16>(y0), 0.f); y0 *= y0;
+                                y1 = fmaxf(rnd<__nv_bfloat16>(y1), 0.f); y1 *= y1;
+                            }
                             if constexpr (EPI == kAddResidual) {
                                 const float2 r = __bfloat1622float2(r2[k]);
                                 y0 = rnd<__nv_bfloat16>(y0) + r.x;
@@ -316,12 +320,14 @@ extern "C" int cvb_gemm_bf16_tcgen05(void* out, const void* a, const void* w, co
     if (mode == 1) return launch_gemm<256, 4, kSwiglu>(ma, mw, mo, p, stream);
     if (mode == 0) return tile_n == 256 ? launch_gemm<256, 4, kPlain>(ma, mw, mo, p, stream) : launch_gemm<128, 6, kPlain>(ma, mw, mo, p, stream);
     if (mode == 2) return tile_n == 256 ? launch_gemm<256, 4, kAddResidual>(ma, mw, mo, p, stream) : launch_gemm<128, 6, kAddResidual>(ma, mw, mo, p, stream);
+    if (mode == 3) return tile_n == 256 ? launch_gemm<256, 4, kRelu2>(ma, mw, mo, p, stream) : launch_gemm<128, 6, kRelu2>(ma, mw, mo, p, stream);
     return CVB_E_SHAPE;
 }
 
 // The grouped form: A [M, K] holds the rows of E experts in segments that start on multiples of 128 rows; row tile i
 // belongs to expert tile_expert[i] (device memory, negative: no rows); W [E * N, K] holds the experts' matrices one below
-// the other.  mode 0: C[M, N] = A W_e^T per tile;  mode 1: C[M, N / 2] = silu(A Wg_e^T) * (A Wu_e^T), W_e = [Wg_e; Wu_e].
+// the other.  mode 0: C[M, N] = A W_e^T per tile;  mode 1: C[M, N / 2] = silu(A Wg_e^T) * (A Wu_e^T), W_e = [Wg_e; Wu_e];
+// mode 3: C[M, N] = relu(A W_e^T)^2.
 extern "C" int cvb_gemm_grouped_bf16_tcgen05(void* out, const void* a, const void* w, const int* tile_expert, int M, int N, int E,
                                              int K, int mode, int tile_n, int* err_flag, cudaStream_t stream) {
     if (M == 0) return CVB_OK;
@@ -329,7 +335,7 @@ extern "C" int cvb_gemm_grouped_bf16_tcgen05(void* out, const void* a, const voi
     if (K % 8 || M % kBM) return CVB_E_ALIGN;
     auto al = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
     if (!al(out) || !al(a) || !al(w)) return CVB_E_ALIGN;
-    if (mode != 0 && mode != 1) return CVB_E_SHAPE;
+    if (mode != 0 && mode != 1 && mode != 3) return CVB_E_SHAPE;
     if (mode == 1 && (N % 2)) return CVB_E_SHAPE;
     if (static_cast<int64_t>(E) * N > 2147483647LL) return CVB_E_SIZE;
     GemmParams p{};
@@ -345,5 +351,6 @@ extern "C" int cvb_gemm_grouped_bf16_tcgen05(void* out, const void* a, const voi
     rc = cached_bf16_map(&mo, out, M, p.n_out, 64, 32);
     if (rc != CVB_OK) return rc;
     if (mode == 1) return launch_gemm<256, 4, kSwiglu>(ma, mw, mo, p, stream);
+    if (mode == 3) return tile_n == 256 ? launch_gemm<256, 4, kRelu2>(ma, mw, mo, p, stream) : launch_gemm<128, 6, kRelu2>(ma, mw, mo, p, stream);
     return tile_n == 256 ? launch_gemm<256, 4, kPlain>(ma, mw, mo, p, stream) : launch_gemm<128, 6, kPlain>(ma, mw, mo, p, stream);
 }

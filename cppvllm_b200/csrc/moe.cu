@@ -3,6 +3,10 @@
 //   route_topk     : z = x Wr^T + b in float (x may be bf16; Wr and b are float); top-k by z
 //                    (of equal z the lower index first), weights exp(z_e) / sum over the k winners of exp(z_c):
 //                    ids[t, k], weights[t, k], k in order of falling logit.  One warp per token.
+//                    `mode` 1: weights scale * exp(z_e) / sum over ALL experts of exp(z_c) instead (not renormalised over the
+//                    winners).  Rows of Wr behind the E experts' (`extra` of them) are not experts: their raw products
+//                    leave as extra_out[t, :] (a gate per token that shares the router's pass over x).
+//   With `gated` = 0 an expert is  Wd_e ( T(relu(T(Wu_e x))^2) )  and Wgu holds [E, ff, D].
 //   An expert is  Wd_e ( T(act(Wg_e x) * (Wu_e x)) ),  act(z) = z * sigmoid(z);  the layer's output is
 //   y[t] = T( sum_k weights[t, k] * expert_{ids[t, k]}(x[t]) ).  Wgu is [E, 2 ff, D] (gate rows over up rows), Wd is
 //   [E, D, ff].  Products and the weighted sum are float; the gated activation is rounded to T once, as the input of a
@@ -26,7 +30,8 @@ constexpr int kRouteWarps = 4;
 template <typename T>
 __global__ void __launch_bounds__(kRouteWarps * 32)
 route_topk_kernel(int* __restrict__ ids, float* __restrict__ weights, const T* __restrict__ x, const float* __restrict__ wr,
-                  const float* __restrict__ bias, int n_tokens, int D, int E, int top) {
+                  const float* __restrict__ bias, int n_tokens, int D, int E, int top, int mode, float scale, int extra,
+                  float* __restrict__ extra_out) {
     pdl_trigger();
     pdl_wait();
     extern __shared__ float smem[];                     // [kRouteWarps][E]
@@ -42,7 +47,22 @@ route_topk_kernel(int* __restrict__ ids, float* __restrict__ weights, const T* _
         d = warp_sum(d);
         if (lane == 0) z[e] = d + (bias ? bias[e] : 0.f);
     }
+    for (int e = 0; e < extra; ++e) {
+        const float* w = wr + static_cast<int64_t>(E + e) * D;
+        float d = 0.f;
+        for (int i = lane; i < D; i += 32) d = fmaf(to_float(xr[i]), w[i], d);
+        d = warp_sum(d);
+        if (lane == 0) extra_out[t * extra + e] = d;
+    }
     __syncwarp();
+    float all = 0.f;                                    // mode 1: the sum over all experts, against the largest logit
+    if (mode == 1) {
+        float big = -INFINITY;
+        for (int e = lane; e < E; e += 32) big = fmaxf(big, z[e]);
+        big = warp_max(big);
+        for (int e = lane; e < E; e += 32) all += expf(z[e] - big);
+        all = warp_sum(all);
+    }
     float z_first = 0.f, sum = 0.f;
     for (int k = 0; k < top; ++k) {
         float best = -INFINITY;
@@ -67,7 +87,7 @@ route_topk_kernel(int* __restrict__ ids, float* __restrict__ weights, const T* _
         }
         __syncwarp();
     }
-    const float inv = 1.f / sum;
+    const float inv = mode == 1 ? scale / all : 1.f / sum;
     for (int k = lane; k < top; k += 32) weights[t * top + k] *= inv;     // lane 0's writes are visible after the syncwarp
 }
 
@@ -102,7 +122,7 @@ template <> __device__ __forceinline__ float dot8_of<__nv_bfloat16>(const __nv_b
 template <typename T>
 __global__ void __launch_bounds__(kExpertThreads)
 expert_hidden_kernel(T* __restrict__ hid, const T* __restrict__ x, const int* __restrict__ ids, const T* __restrict__ wgu,
-                     int D, int F, int E, int top, int per_block, int* __restrict__ err) {
+                     int D, int F, int E, int top, int per_block, int gated, int* __restrict__ err) {
     pdl_trigger();
     pdl_wait();
     extern __shared__ __align__(16) float smem[];
@@ -117,7 +137,7 @@ expert_hidden_kernel(T* __restrict__ hid, const T* __restrict__ x, const int* __
     }
     for (int i = threadIdx.x; i < D; i += kExpertThreads) xs[i] = to_float(x[t * D + i]);
     __syncthreads();
-    const T* g_rows = wgu + static_cast<int64_t>(e) * 2 * F * D;
+    const T* g_rows = wgu + static_cast<int64_t>(e) * (gated ? 2 : 1) * F * D;
     const T* u_rows = g_rows + static_cast<int64_t>(F) * D;
     const int f0 = blockIdx.y * per_block, f1 = min(F, f0 + per_block);
     const bool wide = rows_by_16_bytes<T>(wgu, D);
@@ -125,14 +145,24 @@ expert_hidden_kernel(T* __restrict__ hid, const T* __restrict__ x, const int* __
         const T* gr = g_rows + static_cast<int64_t>(f) * D;
         const T* ur = u_rows + static_cast<int64_t>(f) * D;
         float g = 0.f, u = 0.f;
-        for (int i = lane; i < D; i += 32) {
-            const float xv = xs[i];
-            g = fmaf(xv, to_float(gr[i]), g);
-            u = fmaf(xv, to_float(ur[i]), u);
+        if (gated) {
+            for (int i = lane; i < D; i += 32) {
+                const float xv = xs[i];
+                g = fmaf(xv, to_float(gr[i]), g);
+                u = fmaf(xv, to_float(ur[i]), u);
+            }
+            g = warp_sum(g);
+            u = warp_sum(u);
+            if (lane == 0) hid[pair * F + f] = from_float<T>(silu_exact<T>(g) * u);
+        } else {
+            if (wide) {
+                for (int i = lane * 8; i < D; i += 256) g = dot8_of<T>(gr + i, xs + i, g);
+            } else {
+                for (int i = lane; i < D; i += 32) g = fmaf(xs[i], to_float(gr[i]), g);
+            }
+            g = fmaxf(rnd<T>(warp_sum(g)), 0.f);
+            if (lane == 0) hid[pair * F + f] = from_float<T>(g * g);
         }
-        g = warp_sum(g);
-        u = warp_sum(u);
-        if (lane == 0) hid[pair * F + f] = from_float<T>(silu_exact<T>(g) * u);
     }
 }
 
@@ -250,20 +280,22 @@ __global__ void combine_pairs_kernel(__nv_bfloat16* __restrict__ y, const __nv_b
 using namespace cvb;
 
 extern "C" int cvb_route_topk(int* ids, float* weights, const void* x, const float* wr, const float* bias, int T, int D, int E,
-                              int top, int dtype, cudaStream_t stream) {
+                              int top, int mode, float scale, int extra, float* extra_out, int dtype, cudaStream_t stream) {
     if (T == 0) return CVB_OK;
-    if (T < 0 || D <= 0 || E <= 0 || top <= 0) return CVB_E_SIZE;
+    if (T < 0 || D <= 0 || E <= 0 || top <= 0 || extra < 0 || (extra > 0 && extra_out == nullptr)) return CVB_E_SIZE;
+    if (mode != 0 && mode != 1) return CVB_E_SHAPE;
     if (top > E || E > 2048) return CVB_E_SHAPE;
     const size_t smem = static_cast<size_t>(kRouteWarps) * E * sizeof(float);
 #define CALL(TY) launch_kernel(route_topk_kernel<TY>, dim3((T + kRouteWarps - 1) / kRouteWarps), dim3(kRouteWarps * 32), smem, \
-                               stream, ids, weights, (const TY*)x, wr, bias, T, D, E, top)
+                               stream, ids, weights, (const TY*)x, wr, bias, T, D, E, top, mode, scale, extra, extra_out)
     CVB_DISPATCH_DTYPE(dtype, CALL);
 #undef CALL
     return launch_status();
 }
 
 extern "C" int cvb_expert_rows(void* y, void* hid, const void* x, const int* ids, const float* weights, const void* wgu,
-                               const void* wd, int T, int D, int F, int E, int top, int dtype, int* err_flag, cudaStream_t stream) {
+                               const void* wd, int T, int D, int F, int E, int top, int gated, int dtype, int* err_flag,
+                               cudaStream_t stream) {
     if (T == 0) return CVB_OK;
     if (T < 0 || D <= 0 || F <= 0 || E <= 0 || top <= 0) return CVB_E_SIZE;
     if (static_cast<size_t>(D) * sizeof(float) > 160 * 1024 || static_cast<size_t>(F) * sizeof(float) > 160 * 1024) return CVB_E_SIZE;
@@ -283,7 +315,7 @@ extern "C" int cvb_expert_rows(void* y, void* hid, const void* x, const int* ids
         if (smem2 > 48 * 1024)                                                                                           \
             cudaFuncSetAttribute(expert_down_kernel<TY>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem2);       \
         launch_kernel(expert_hidden_kernel<TY>, dim3((unsigned)pairs, (F + f_per - 1) / f_per), dim3(kExpertThreads), smem1,  \
-                      stream, (TY*)hid, (const TY*)x, ids, (const TY*)wgu, D, F, E, top, f_per, err_flag);                \
+                      stream, (TY*)hid, (const TY*)x, ids, (const TY*)wgu, D, F, E, top, f_per, gated, err_flag);                \
         launch_kernel(expert_down_kernel<TY>, dim3(T, (D + d_per - 1) / d_per), dim3(kExpertThreads), smem2, stream,      \
                       (TY*)y, (const TY*)hid, ids, weights, (const TY*)wd, D, F, E, top, d_per);                          \
     } while (0)

@@ -102,7 +102,7 @@ def core():
     if _core is None:
         lib = load_library("core")
         for name in ("cvb_embed", "cvb_rmsnorm", "cvb_add_rmsnorm", "cvb_add", "cvb_swiglu", "cvb_gather_rows",
-                     "cvb_qk_norm_rope_kv", "cvb_paged_attention_general", "cvb_sample", "cvb_sample_chunked",
+                     "cvb_qk_norm_rope_kv", "cvb_paged_attention_general", "cvb_paged_attention_entries", "cvb_sample", "cvb_sample_chunked",
                      "cvb_feed_tokens"):
             getattr(lib, name).restype = c_int
         _core = lib
@@ -324,17 +324,158 @@ def bias_act(out: torch.Tensor, x: torch.Tensor, bias: Optional[torch.Tensor], a
     return out
 
 
-def gated_norm(out: torch.Tensor, o: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, groups: int, eps: float) -> torch.Tensor:
-    """out[t, g, :] = RMSNorm(o[t, g, :]) * weight * sigmoid(gate[t, g, :]) over `groups` groups of weight.numel() elements;
+def gated_norm(out: torch.Tensor, o: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, groups: int, eps: float,
+               gate_act: str = "sigmoid") -> torch.Tensor:
+    """out[t, g, :] = RMSNorm(o[t, g, :]) * weight * sigmoid(gate[t, g, :]) (or * silu(gate): `gate_act` = "silu") over `groups` groups of weight.numel() elements;
     o float32 [T, groups * G]; gate a view of [T, groups * G] columns inside rows of gate.stride(0) elements."""
     _cuda(out, o, gate, weight); _contig(out, o, weight)
     T = o.shape[0]
     G = weight.numel()
+    if gate_act not in ("sigmoid", "silu"):
+        raise KernelError("gated_norm: gate_act is sigmoid or silu")
     if (o.dtype != torch.float32 or o.shape[1] != groups * G or out.shape != o.shape or gate.dtype != out.dtype or gate.dim() != 2
             or gate.shape != o.shape or gate.stride(1) != 1 or weight.dtype != torch.float32):
         raise KernelError("gated_norm: o float32 [T, groups * G]; out and gate [T, groups * G] of the activations' type; weight float32 [G]")
     _check(_resid32_lib().cvb_gated_norm(_ptr(out), _ptr(o), _ptr(gate), c_int(gate.stride(0)), _ptr(weight), c_int(T), c_int(groups),
-                                         c_int(G), c_float(eps), c_int(dtype_code(out.dtype)), _stream()), "gated_norm")
+                                         c_int(G), c_float(eps), c_int(1 if gate_act == "silu" else 0), c_int(dtype_code(out.dtype)), _stream()), "gated_norm")
+    return out
+
+
+# ---- sublayers wrapped twice, read through a convolution and left through a gate; attention with whole-projection norms ----
+
+_sandwich = None
+
+
+def _sandwich_lib():
+    global _sandwich
+    if _sandwich is None:
+        lib = load_library("sandwich")
+        for name in ("cvb_input_conv", "cvb_gated_norm_add", "cvb_glu_clamped", "cvb_add_gated_rows", "cvb_wide_qk_prep"):
+            getattr(lib, name).restype = c_int
+        _sandwich = lib
+    return _sandwich
+
+
+def input_conv(out: torch.Tensor, a: torch.Tensor, taps: torch.Tensor, state: torch.Tensor, hist_off: int, seq_of_token, cu_seqlens,
+               state_slots) -> torch.Tensor:
+    """out[t, c] = a[t, c] + sum_j taps[c, j] * a[t - K + 1 + j, c]: a causal convolution over time per channel, added to its
+    input.  What lies before the step's portion comes from the request's history: K - 1 rows of D floats from `hist_off` on in
+    the request's state row (oldest first)."""
+    _cuda(out, a, taps, state, seq_of_token, cu_seqlens, state_slots); _contig(out, a, taps, seq_of_token, cu_seqlens, state_slots)
+    sp, sf, n_slots = _state_args(state)
+    T, D = a.shape
+    if out.shape != a.shape or out.dtype != a.dtype or taps.dtype != torch.float32 or taps.dim() != 2 or taps.shape[0] != D:
+        raise KernelError("input_conv: out like a [T, D]; taps float32 [D, K]")
+    _check(_sandwich_lib().cvb_input_conv(_ptr(out), _ptr(a), _ptr(taps), c_int(T), c_int(D), c_int(taps.shape[1]), sp, sf,
+                                          c_int64(hist_off), _ptr(seq_of_token), _ptr(cu_seqlens), _ptr(state_slots), c_int(n_slots),
+                                          c_int(dtype_code(a.dtype)), _ptr(error_flag(a.device)), _stream()), "input_conv")
+    return out
+
+
+def gated_norm_add(h: torch.Tensor, y: torch.Tensor, weight: torch.Tensor, eps: float, gate: Optional[torch.Tensor] = None,
+                   gate_bias: Optional[torch.Tensor] = None, next_weight: Optional[torch.Tensor] = None, next_eps: float = 0.0,
+                   next_out: Optional[torch.Tensor] = None, history=None) -> torch.Tensor:
+    """h (float32 [T, D]) += RMSNorm(y * sigmoid(gate + gate_bias)) * weight.  With `next_weight` also next_out = RMSNorm(h) *
+    next_weight (the activations' type).  `history` = (a, taps, state, hist_off, seq_of_token, cu_seqlens, state_slots): the
+    last taps - 1 rows of `a` of every request's portion (older ones from the old history) become its convolution history;
+    `next_out` must not be `a` then."""
+    _cuda(h, y, weight, gate, gate_bias, next_weight, next_out); _contig(h, y, weight, gate, gate_bias, next_weight, next_out)
+    T, D = h.shape
+    if (h.dtype != torch.float32 or y.shape != h.shape or weight.dtype != torch.float32 or weight.numel() != D
+            or (gate is not None and (gate.shape != h.shape or gate.dtype != y.dtype))
+            or (gate_bias is not None and (gate_bias.dtype != torch.float32 or gate_bias.numel() != D))
+            or (next_weight is not None and (next_out is None or next_out.shape != h.shape or next_out.dtype != y.dtype
+                                             or next_weight.dtype != torch.float32 or next_weight.numel() != D))):
+        raise KernelError("gated_norm_add: h float32 [T, D]; y, gate, next_out [T, D] of the activations' type; weights float32 [D]")
+    a = st = sot = cu = slots = None
+    sf, n_slots, hist_off, taps = c_int64(0), 0, 0, 0
+    if history is not None:
+        a, taps, state, hist_off, sot, cu, slots = history
+        _cuda(a, state, sot, cu, slots); _contig(a, sot, cu, slots)
+        st, sf, n_slots = _state_args(state)
+        if a.shape != h.shape or a.dtype != y.dtype or (next_out is not None and next_out.data_ptr() == a.data_ptr()):
+            raise KernelError("gated_norm_add: the history's rows are [T, D] of the activations' type, apart from next_out")
+    _check(_sandwich_lib().cvb_gated_norm_add(
+        _ptr(h), _ptr(y), _ptr(gate), _ptr(gate_bias), _ptr(weight), c_float(eps), _ptr(next_weight), c_float(next_eps), _ptr(next_out),
+        c_int(T), c_int(D), _ptr(a), st if st is not None else _ptr(None), sf, c_int64(hist_off), c_int(int(taps)), _ptr(sot), _ptr(cu),
+        _ptr(slots), c_int(n_slots), c_int(dtype_code(y.dtype)), _stream()), "gated_norm_add")
+    return h
+
+
+def glu_clamped(out: torch.Tensor, gate_up: torch.Tensor, limit: float, alpha: float) -> torch.Tensor:
+    """out = g * sigmoid(alpha * g) * (u + 1), g = min(gate, limit), u = clamp(up, -limit, limit); gate_up [T, 2 I] (gate columns, then up)."""
+    _cuda(out, gate_up); _contig(out, gate_up)
+    T, I = out.shape
+    if gate_up.shape != (T, 2 * I) or gate_up.dtype != out.dtype:
+        raise KernelError("glu_clamped: gate_up must be [T, 2I] for out [T, I]")
+    _check(_sandwich_lib().cvb_glu_clamped(_ptr(out), _ptr(gate_up), c_int(T), c_int(I), c_float(limit), c_float(alpha),
+                                           c_int(dtype_code(out.dtype)), _stream()), "glu_clamped")
+    return out
+
+
+def add_gated_rows(y: torch.Tensor, s: torch.Tensor, z: torch.Tensor) -> torch.Tensor:
+    """y[t, :] += sigmoid(z[t]) * s[t, :]; z float32, one element per row (a column of a wider float32 tensor will do)."""
+    _cuda(y, s, z); _contig(y, s)
+    T, D = y.shape
+    if s.shape != y.shape or s.dtype != y.dtype or z.dtype != torch.float32 or z.dim() != 1 or z.shape[0] != T:
+        raise KernelError("add_gated_rows: s like y [T, D]; z float32 [T]")
+    _check(_sandwich_lib().cvb_add_gated_rows(_ptr(y), _ptr(s), _ptr(z), c_int(z.stride(0) if T > 0 else 1), c_int(T), c_int(D),
+                                              c_int(dtype_code(y.dtype)), _stream()), "add_gated_rows")
+    return y
+
+
+def wide_qk_prep(q_out: torch.Tensor, packed: torch.Tensor, q_weight: torch.Tensor, positions: torch.Tensor, eps: float,
+                 temp_coef: float, temp_every: int, num_kv_heads: int, dim: int, vdim: int, pages: Optional[torch.Tensor] = None,
+                 k_weight: Optional[torch.Tensor] = None, slots: Optional[torch.Tensor] = None, page_size: int = 1) -> torch.Tensor:
+    """q_out = RMSNorm over the WHOLE query projection (the first q_out.shape[1] columns of `packed`) * q_weight * (1 + temp_coef *
+    ln(floor((p + 1) / temp_every) + 1)) (temp_every = 0: no temperature).  With `pages`: the key projection behind the queries
+    is normed the same way with k_weight and written, with the value projection behind it, into pages [page, kv head, slot,
+    dim + vdim] at `slots`."""
+    _cuda(q_out, packed, q_weight, positions, pages, k_weight, slots); _contig(q_out, packed, q_weight, positions, pages, k_weight, slots)
+    T, nq = q_out.shape
+    write = pages is not None
+    if (q_out.dtype != packed.dtype or packed.shape[0] != T or q_weight.dtype != torch.float32 or q_weight.numel() != nq
+            or positions.dtype != torch.int32
+            or (write and (pages.dtype != packed.dtype or k_weight is None or k_weight.dtype != torch.float32
+                           or k_weight.numel() != num_kv_heads * dim or slots is None or slots.dtype != torch.int32))):
+        raise KernelError("wide_qk_prep: q_out [T, nq] and pages like packed; weights float32; positions, slots int32")
+    num_pages = pages.numel() // (num_kv_heads * page_size * (dim + vdim)) if write else 0
+    _check(_sandwich_lib().cvb_wide_qk_prep(
+        _ptr(q_out), _ptr(pages), _ptr(packed), c_int(T), c_int(packed.shape[1]), _ptr(q_weight), _ptr(k_weight), _ptr(positions),
+        _ptr(slots), c_int(nq), c_int(num_kv_heads), c_int(dim), c_int(vdim), c_int(page_size), c_int64(num_pages), c_float(eps),
+        c_float(temp_coef), c_int(temp_every), c_int(1 if write else 0), c_int(dtype_code(packed.dtype)),
+        _ptr(error_flag(packed.device)), _stream()), "wide_qk_prep")
+    return q_out
+
+
+def attn_bias_supported(dtype: torch.dtype, num_heads: int, num_kv_heads: int, dim: int, vdim: int) -> bool:
+    """Whether the tensor-core kernel takes the shape (csrc/attention_bias.cu)."""
+    return False
+
+
+def paged_attention_entries(out: torch.Tensor, q: torch.Tensor, pages: torch.Tensor, block_tables: torch.Tensor,
+                            seq_of_token: torch.Tensor, positions: torch.Tensor, num_heads: int, num_kv_heads: int, dim: int,
+                            vdim: int, page_size: int, scale: float, bias: Optional[torch.Tensor] = None, window: int = 0,
+                            num_tokens: Optional[int] = None) -> torch.Tensor:
+    """The general attention kernel (one block per token and query head, any sizes, float32 or bf16) over pages [page, kv head,
+    slot, dim + vdim] whose entries hold a key and, behind it, its value.  `bias` float32 [H, L]: the score of key j for the
+    token at position p receives bias[h, min(p - j, L - 1)] after the scale."""
+    _cuda(out, q, pages, block_tables, seq_of_token, positions, bias); _contig(out, q, pages, block_tables, seq_of_token, positions, bias)
+    T = q.shape[0] if num_tokens is None else num_tokens
+    if q.dtype != pages.dtype or out.dtype != q.dtype:
+        raise KernelError("paged_attention_entries: q, out and the cache pages must share one element type")
+    if block_tables.dtype != torch.int32 or block_tables.dim() != 2 or seq_of_token.dtype != torch.int32 or positions.dtype != torch.int32:
+        raise KernelError("paged_attention_entries: block_tables int32 [S, W]; seq_of_token and positions int32")
+    if num_heads % num_kv_heads or out.numel() < T * num_heads * vdim:
+        raise KernelError("paged_attention_entries: head counts or the size of out do not fit")
+    if bias is not None and (bias.dtype != torch.float32 or bias.dim() != 2 or bias.shape[0] != num_heads):
+        raise KernelError("paged_attention_entries: bias is float32 [H, L]")
+    num_pages = pages.numel() // (num_kv_heads * page_size * (dim + vdim))
+    _check(core().cvb_paged_attention_entries(
+        _ptr(out), _ptr(q), _ptr(pages), _ptr(block_tables), c_int(block_tables.shape[1]), _ptr(seq_of_token), _ptr(positions),
+        c_int(T), c_int(num_heads), c_int(num_kv_heads), c_int(dim), c_int(vdim), c_int(page_size), c_int(window),
+        c_int(q.shape[1]), c_float(scale), c_int(num_pages), _ptr(bias), c_int(bias.shape[1] if bias is not None else 0),
+        c_int(dtype_code(q.dtype)), _ptr(error_flag(q.device)), _stream()), "paged_attention_entries")
     return out
 
 
@@ -463,16 +604,18 @@ def lightning_scan(out: torch.Tensor, qf: torch.Tensor, kf: torch.Tensor, vf: to
 
 def delta_prep(qn, kn, vv, gg, bb, packed: torch.Tensor, qkv_off: int, conv_w: torch.Tensor, a: torch.Tensor, dt_bias: torch.Tensor,
                a_log: torch.Tensor, b: torch.Tensor, state: torch.Tensor, conv_off: int, seq_of_token, cu_seqlens, state_slots,
-               num_heads: int, num_kv_heads: int, dim: int, vdim: int) -> None:
-    """Per token: convolutions with silu, unit q and k, sigmoid(b), the decay; all outputs float32 (see csrc/recurrent.cu)."""
+               num_heads: int, num_kv_heads: int, dim: int, vdim: int, decay_dim: Optional[int] = None) -> None:
+    """Per token: convolutions with silu, unit q and k, sigmoid(b), the decay; all outputs float32 (see csrc/recurrent.cu).
+    `decay_dim`: decays per head, `dim` (one per key channel, the default) or 1 (one per head)."""
     _cuda(qn, kn, vv, gg, bb, packed, conv_w, a, dt_bias, a_log, b, state, seq_of_token, cu_seqlens, state_slots)
     _contig(qn, kn, vv, gg, bb, packed, conv_w, a, dt_bias, a_log, b, seq_of_token, cu_seqlens, state_slots)
     sp, sf, n_slots = _state_args(state)
     T = packed.shape[0]
     H, G = num_heads, num_kv_heads
     C = 2 * G * dim + H * vdim
-    for t_, n_ in ((qn, T * G * dim), (kn, T * G * dim), (vv, T * H * vdim), (gg, T * H * dim), (bb, T * H), (a, T * H * dim), (b, T * H),
-                   (dt_bias, H * dim), (a_log, H)):
+    gd = dim if decay_dim is None else int(decay_dim)
+    for t_, n_ in ((qn, T * G * dim), (kn, T * G * dim), (vv, T * H * vdim), (gg, T * H * gd), (bb, T * H), (a, T * H * gd), (b, T * H),
+                   (dt_bias, H * gd), (a_log, H)):
         if t_.dtype != torch.float32 or t_.numel() != n_:
             raise KernelError("delta_prep: float32 buffers of the sizes the head counts give")
     if conv_w.dtype != torch.float32 or conv_w.dim() != 2 or conv_w.shape[0] != C:
@@ -480,7 +623,7 @@ def delta_prep(qn, kn, vv, gg, bb, packed: torch.Tensor, qkv_off: int, conv_w: t
     _check(_recurrent_lib().cvb_delta_prep(
         _ptr(qn), _ptr(kn), _ptr(vv), _ptr(gg), _ptr(bb), _ptr(packed), c_int(T), c_int(packed.shape[1]), c_int(qkv_off), _ptr(conv_w),
         c_int(conv_w.shape[1]), _ptr(a), _ptr(dt_bias), _ptr(a_log), _ptr(b), sp, sf, c_int64(conv_off), _ptr(seq_of_token),
-        _ptr(cu_seqlens), _ptr(state_slots), c_int(n_slots), c_int(H), c_int(G), c_int(dim), c_int(vdim), c_int(dtype_code(packed.dtype)),
+        _ptr(cu_seqlens), _ptr(state_slots), c_int(n_slots), c_int(H), c_int(G), c_int(dim), c_int(vdim), c_int(gd), c_int(dtype_code(packed.dtype)),
         _ptr(error_flag(packed.device)), _stream()), "delta_prep")
 
 
@@ -495,15 +638,17 @@ def conv_history(state: torch.Tensor, conv_off: int, packed: torch.Tensor, qkv_o
 
 
 def delta_scan(out, qn, kn, vv, gg, bb, state: torch.Tensor, cu_seqlens, state_slots, num_seqs: int, num_heads: int, num_kv_heads: int,
-               dim: int, vdim: int) -> torch.Tensor:
-    """Per request and head: S <- diag(g) S; u = b (v - S^T k); S <- S + k u^T; out = S^T q.  out float32 [T, H * vdim]."""
+               dim: int, vdim: int, decay_dim: Optional[int] = None) -> torch.Tensor:
+    """Per request and head: S <- diag(g) S; u = b (v - S^T k); S <- S + k u^T; out = S^T q.  out float32 [T, H * vdim].
+    gg is [T, H * dim], or [T, H] with `decay_dim` = 1 (one decay per head: S <- g S)."""
     _cuda(out, qn, kn, vv, gg, bb, state, cu_seqlens, state_slots); _contig(out, qn, kn, vv, gg, bb, cu_seqlens, state_slots)
     sp, sf, n_slots = _state_args(state)
     if out.dtype != torch.float32:
         raise KernelError("delta_scan: out is float32")
     _check(_recurrent_lib().cvb_delta_scan(_ptr(out), _ptr(qn), _ptr(kn), _ptr(vv), _ptr(gg), _ptr(bb), sp, sf, _ptr(cu_seqlens),
                                            _ptr(state_slots), c_int(n_slots), c_int(num_seqs), c_int(num_heads), c_int(num_kv_heads),
-                                           c_int(dim), c_int(vdim), _ptr(error_flag(out.device)), _stream()), "delta_scan")
+                                           c_int(dim), c_int(vdim), c_int(dim if decay_dim is None else int(decay_dim)),
+                                           _ptr(error_flag(out.device)), _stream()), "delta_scan")
     return out
 
 
@@ -596,36 +741,43 @@ def _moe_lib():
 
 
 def route_topk(ids: torch.Tensor, weights: torch.Tensor, x: torch.Tensor, router: torch.Tensor,
-               bias: Optional[torch.Tensor]) -> None:
-    """ids, weights [T, top]: the `top` largest of x @ router^T + bias (float32 arithmetic) and the softmax over them."""
-    _cuda(ids, weights, x, router, bias); _contig(ids, weights, x, router, bias)
+               bias: Optional[torch.Tensor], over_all: bool = False, scale: float = 1.0,
+               extra_out: Optional[torch.Tensor] = None) -> None:
+    """ids, weights [T, top]: the `top` largest of x @ router^T + bias (float32 arithmetic) and the softmax over them; with
+    `over_all` the weights are `scale` times the winners' shares of the softmax over ALL experts instead.  `extra_out`
+    float32 [T, n]: the last n rows of `router` are not experts, their products with x leave there unchanged."""
+    _cuda(ids, weights, x, router, bias, extra_out); _contig(ids, weights, x, router, bias, extra_out)
     T, D = x.shape
-    E = router.shape[0]
+    extra = 0 if extra_out is None else extra_out.shape[1]
+    E = router.shape[0] - extra
     top = ids.shape[1]
+    if extra_out is not None and (extra_out.dtype != torch.float32 or extra_out.shape[0] != T or E <= 0):
+        raise KernelError("route_topk: extra_out float32 [T, n] with n below the router's rows")
     if (ids.dtype != torch.int32 or weights.dtype != torch.float32 or router.dtype != torch.float32 or router.shape[1] != D
             or ids.shape != (T, top) or weights.shape != (T, top) or (bias is not None and (bias.dtype != torch.float32 or bias.numel() != E))):
         raise KernelError("route_topk: ids int32 and weights float32 [T, top]; router float32 [E, D]; bias float32 [E]")
     _check(_moe_lib().cvb_route_topk(_ptr(ids), _ptr(weights), _ptr(x), _ptr(router), _ptr(bias), c_int(T), c_int(D), c_int(E),
-                                     c_int(top), c_int(dtype_code(x.dtype)), _stream()), "route_topk")
+                                     c_int(top), c_int(1 if over_all else 0), c_float(scale), c_int(extra), _ptr(extra_out),
+                                     c_int(dtype_code(x.dtype)), _stream()), "route_topk")
 
 
 def expert_rows(y: torch.Tensor, hid: torch.Tensor, x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor,
-                w_gate_up: torch.Tensor, w_down: torch.Tensor) -> torch.Tensor:
+                w_gate_up: torch.Tensor, w_down: torch.Tensor, gated: bool = True) -> torch.Tensor:
     """y[t] = sum_k weights[t, k] * down_e(silu(gate_e x) * up_e x), e = ids[t, k]; w_gate_up [E, 2 ff, D], w_down [E, D, ff];
     `hid` [T * top, ff] is scratch.  Two kernels that read only the chosen experts' weights: for a few tokens, and for
-    float32."""
+    float32.  `gated=False`: an expert is down_e(relu(up_e x)^2) and w_gate_up holds [E, ff, D]."""
     _cuda(y, hid, x, ids, weights, w_gate_up, w_down); _contig(y, hid, x, ids, weights, w_gate_up, w_down)
     T, D = x.shape
     E, F2, _ = w_gate_up.shape
-    F = F2 // 2
+    F = F2 // 2 if gated else F2
     top = ids.shape[1]
     if (y.shape != x.shape or y.dtype != x.dtype or w_gate_up.dtype != x.dtype or w_down.dtype != x.dtype or hid.dtype != x.dtype
-            or w_gate_up.shape != (E, 2 * F, D) or w_down.shape != (E, D, F) or ids.dtype != torch.int32 or hid.numel() < T * top * F
+            or w_gate_up.shape != (E, (2 if gated else 1) * F, D) or w_down.shape != (E, D, F) or ids.dtype != torch.int32 or hid.numel() < T * top * F
             or weights.dtype != torch.float32 or ids.shape != weights.shape or ids.shape[0] != T):
         raise KernelError("expert_rows: x, y [T, D], hid [T * top, ff], w_gate_up [E, 2 ff, D] and w_down [E, D, ff] of one element "
                           "type; ids int32 and weights float32 [T, top]")
     _check(_moe_lib().cvb_expert_rows(_ptr(y), _ptr(hid), _ptr(x), _ptr(ids), _ptr(weights), _ptr(w_gate_up), _ptr(w_down), c_int(T),
-                                      c_int(D), c_int(F), c_int(E), c_int(top), c_int(dtype_code(x.dtype)),
+                                      c_int(D), c_int(F), c_int(E), c_int(top), c_int(1 if gated else 0), c_int(dtype_code(x.dtype)),
                                       _ptr(error_flag(x.device)), _stream()), "expert_rows", kernels=2)
     return y
 
@@ -640,7 +792,8 @@ def grouped_rows_tcgen05(num_tokens: int, top: int, num_experts: int) -> int:
     return ((num_tokens * top + 127) // 128 + num_experts) * 128
 
 
-def experts_grouped_tcgen05(y, x, ids, weights, w_gate_up, w_down, tile_expert, row_token, slot_of, xs, hid, rows) -> torch.Tensor:
+def experts_grouped_tcgen05(y, x, ids, weights, w_gate_up, w_down, tile_expert, row_token, slot_of, xs, hid, rows,
+                            gated: bool = True) -> torch.Tensor:
     """More tokens on the tcgen05 tensor cores: the pairs are sorted by expert into segments that start on multiples of
     128 rows (device side), the tokens' rows are gathered into that order, and two grouped products (the first with the
     gated activation as its epilogue) run on csrc/gemm_tcgen05.cu's kernel; the last kernel adds a token's expert outputs
@@ -651,10 +804,10 @@ def experts_grouped_tcgen05(y, x, ids, weights, w_gate_up, w_down, tile_expert, 
     _contig(y, x, ids, weights, w_gate_up, w_down, tile_expert, row_token, slot_of, xs, hid, rows)
     T, D = x.shape
     E, F2, _ = w_gate_up.shape
-    F, top = F2 // 2, ids.shape[1]
+    F, top = (F2 // 2 if gated else F2), ids.shape[1]
     R = grouped_rows_tcgen05(T, top, E)
     bf = torch.bfloat16
-    if (any(t.dtype != bf for t in (y, x, w_gate_up, w_down, xs, hid, rows)) or y.shape != x.shape or w_gate_up.shape != (E, 2 * F, D)
+    if (any(t.dtype != bf for t in (y, x, w_gate_up, w_down, xs, hid, rows)) or y.shape != x.shape or w_gate_up.shape != (E, F2, D)
             or w_down.shape != (E, D, F) or ids.dtype != torch.int32 or weights.dtype != torch.float32 or ids.shape != weights.shape
             or any(t.dtype != torch.int32 for t in (tile_expert, row_token, slot_of)) or tile_expert.numel() < R // 128
             or row_token.numel() < R or slot_of.numel() < T * top or xs.numel() < R * D or hid.numel() < R * F or rows.numel() < R * D):
@@ -669,8 +822,14 @@ def experts_grouped_tcgen05(y, x, ids, weights, w_gate_up, w_down, tile_expert, 
                                             c_int(R // 128), err, _stream()), "sort_pairs_padded")
     xs2, hid2, rows2 = xs.view(-1)[:R * D].view(R, D), hid.view(-1)[:R * F].view(R, F), rows.view(-1)[:R * D].view(R, D)
     gather_rows(xs2, x, row_token.view(-1)[:R])
-    _check(_gemm.cvb_gemm_grouped_bf16_tcgen05(_ptr(hid2), _ptr(xs2), _ptr(w_gate_up), _ptr(tile_expert), c_int(R), c_int(2 * F), c_int(E),
-                                               c_int(D), c_int(1), c_int(256), err, _stream()), "gemm_grouped_bf16_tcgen05")
+    if gated:
+        _check(_gemm.cvb_gemm_grouped_bf16_tcgen05(_ptr(hid2), _ptr(xs2), _ptr(w_gate_up), _ptr(tile_expert), c_int(R), c_int(2 * F), c_int(E),
+                                                   c_int(D), c_int(1), c_int(256), err, _stream()), "gemm_grouped_bf16_tcgen05")
+    else:           # the squared relu is the epilogue
+        up_256 = (T * top // 128 + 1) * ((F + 255) // 256)
+        _check(_gemm.cvb_gemm_grouped_bf16_tcgen05(_ptr(hid2), _ptr(xs2), _ptr(w_gate_up), _ptr(tile_expert), c_int(R), c_int(F), c_int(E),
+                                                   c_int(D), c_int(3), c_int(256 if up_256 >= 120 else 128), err, _stream()),
+               "gemm_grouped_bf16_tcgen05")
     tiles_256 = (T * top // 128 + 1) * ((D + 255) // 256)
     _check(_gemm.cvb_gemm_grouped_bf16_tcgen05(_ptr(rows2), _ptr(hid2), _ptr(w_down), _ptr(tile_expert), c_int(R), c_int(D), c_int(E),
                                                c_int(F), c_int(0), c_int(256 if tiles_256 >= 120 else 128), err, _stream()),
@@ -690,15 +849,15 @@ def grouped_experts_preferred(num_pairs: int, num_experts: int, expert_bytes: in
             or (num_pairs >= 3 and expert_bytes >= (64 << 20)))
 
 
-def routed_experts(y, x, ids, weights, w_gate_up, w_down, workspace=None, kernel: str = "") -> torch.Tensor:
+def routed_experts(y, x, ids, weights, w_gate_up, w_down, workspace=None, kernel: str = "", gated: bool = True) -> torch.Tensor:
     """The experts' outputs added up with the router's weights, by the kernels that suit the step: one or two tokens (and
     float32, and sizes that are no multiples of 8) read the chosen experts' weights pair by pair; more go through the
     grouped tcgen05 products (see grouped_experts_preferred).  `workspace` (parts.base.Workspace) lends the scratch;
     without it the scratch is allocated.  `kernel` = "rows" | "tcgen05" fixes the choice (where the shape allows it)."""
     T, D = x.shape
     E, F2, _ = w_gate_up.shape
-    F, top = F2 // 2, ids.shape[1]
-    expert_bytes = 3 * D * F * x.element_size()
+    F, top = (F2 // 2 if gated else F2), ids.shape[1]
+    expert_bytes = (3 if gated else 2) * D * F * x.element_size()
     grouped = kernel == "tcgen05" or (kernel == "" and grouped_experts_preferred(T * top, E, expert_bytes))
     if grouped and experts_grouped_supported(x.dtype, D, F):
         R = grouped_rows_tcgen05(T, top, E)
@@ -711,12 +870,12 @@ def routed_experts(y, x, ids, weights, w_gate_up, w_down, workspace=None, kernel
         slot_of = workspace.rows("moe_slot_of", T, top, torch.int32) if workspace is not None else torch.empty(T * top, dtype=torch.int32, device=x.device)
         return experts_grouped_tcgen05(y, x, ids, weights, w_gate_up, w_down, buf("moe_tile_expert", R, torch.int32),
                                        buf("moe_row_token", R, torch.int32), slot_of, buf(f"moe_xs{D}", R * D, x.dtype),
-                                       buf(f"moe_hid{F}", R * F, x.dtype), buf(f"moe_rows{D}", R * D, x.dtype))
+                                       buf(f"moe_hid{F}", R * F, x.dtype), buf(f"moe_rows{D}", R * D, x.dtype), gated=gated)
     if workspace is not None:
         hid = workspace.rows("moe_hidden", T, top * F, x.dtype)
     else:
         hid = torch.empty((T, top * F), dtype=x.dtype, device=x.device)
-    return expert_rows(y, hid, x, ids, weights, w_gate_up, w_down)
+    return expert_rows(y, hid, x, ids, weights, w_gate_up, w_down, gated=gated)
 
 
 # ---- projection epilogue: per-head norm, rotary, cache write --------------------------------------------------

@@ -8,6 +8,7 @@
 //                    dk^-1/2); b = sigmoid(.); the decay g = exp(-exp(A_h) softplus(a + dt)) per head and key channel
 //   conv_history   : the last taps - 1 raw inputs of every request's portion become the history of its next one
 //   delta_scan     : S <- diag(g) S;  u = b (v - S^T k);  S <- S + k u^T;  o = S^T q      (query/key head h / (H / G))
+//                    The decay is one number per head and key channel, or (`gd` = 1) one number per head: S <- g S.
 //
 // S is [dk, dv] per (request, head), float, in the request's state slot; portions of any length continue where the
 // state stands, one token after the other in the same order of operations, so cutting a sequence changes no bit.
@@ -51,8 +52,9 @@ __global__ void lightning_prep_kernel(float* __restrict__ qf, float* __restrict_
 // The scan of both rules.  A block owns kScanCols columns of S of one (request, head); kScanLanes lanes share a column
 // (rows r * kScanLanes + lane part) and add their parts up by shuffles.  The tokens' q, k (and g), v (and b) travel through
 // two stages of shared memory by cp.async, kScanChunk tokens a stage, so that the next tokens arrive while these are used.
-// DELTA: S <- diag(g) S; u = b (v - S^T k); S <- S + k u^T; o = S^T q.   Else: S <- d S + k v^T; o = S^T q.
-template <int KPT, bool DELTA>
+// MODE 1: S <- diag(g) S; u = b (v - S^T k); S <- S + k u^T; o = S^T q.  MODE 2: the same with one decay per head and token
+// (S <- g S).  MODE 0: S <- d S + k v^T; o = S^T q.
+template <int KPT, int MODE>
 __global__ void __launch_bounds__(kScanThreads)
 recurrent_scan_kernel(float* __restrict__ out, const float* __restrict__ qn, const float* __restrict__ kn, const float* __restrict__ vv,
                       const float* __restrict__ gg, const float* __restrict__ bb, const float* __restrict__ decay,
@@ -62,8 +64,9 @@ recurrent_scan_kernel(float* __restrict__ out, const float* __restrict__ qn, con
     pdl_wait();
     extern __shared__ __align__(16) float sm[];
     constexpr int dkp = KPT * kScanLanes;
-    constexpr int kArrays = DELTA ? 3 : 2;
-    constexpr int kStage = kArrays * kScanChunk * dkp + kScanChunk * kScanCols + kScanChunk;
+    constexpr bool DELTA = MODE != 0;
+    constexpr int kArrays = MODE == 1 ? 3 : 2;
+    constexpr int kStage = kArrays * kScanChunk * dkp + kScanChunk * kScanCols + 2 * kScanChunk;
     const int s = blockIdx.x, h = blockIdx.y, j0 = blockIdx.z * kScanCols;
     const int kvh = h / (H / G);
     const int tid = threadIdx.x, col = tid / kScanLanes, part = tid % kScanLanes, j = j0 + col;
@@ -89,9 +92,10 @@ recurrent_scan_kernel(float* __restrict__ out, const float* __restrict__ qn, con
         const int n = min(kScanChunk, end - t0);
         float* qs = sm + stage * kStage;
         float* ks = qs + kScanChunk * dkp;
-        float* gs = ks + kScanChunk * dkp;                                  // DELTA only
+        float* gs = ks + kScanChunk * dkp;                                  // MODE 1 only
         float* vs = qs + kArrays * kScanChunk * dkp;
         float* bs = vs + kScanChunk * kScanCols;
+        float* g1 = bs + kScanChunk;                                        // MODE 2 only: one decay per token
         if (vec) {
             const int dk4 = dk >> 2;
             for (int idx = tid; idx < n * dk4; idx += kScanThreads) {
@@ -99,7 +103,7 @@ recurrent_scan_kernel(float* __restrict__ out, const float* __restrict__ qn, con
                 const int64_t tok = t0 + tt;
                 cp_async16(qs + tt * dkp + i, qn + (tok * G + kvh) * dk + i, true);
                 cp_async16(ks + tt * dkp + i, kn + (tok * G + kvh) * dk + i, true);
-                if (DELTA) cp_async16(gs + tt * dkp + i, gg + (tok * H + h) * dk + i, true);
+                if (MODE == 1) cp_async16(gs + tt * dkp + i, gg + (tok * H + h) * dk + i, true);
             }
             for (int idx = tid; idx < n * (kScanCols / 4); idx += kScanThreads) {
                 const int tt = idx / (kScanCols / 4), c = (idx - tt * (kScanCols / 4)) * 4;
@@ -111,7 +115,7 @@ recurrent_scan_kernel(float* __restrict__ out, const float* __restrict__ qn, con
                 const int64_t tok = t0 + tt;
                 cp_async4(qs + tt * dkp + i, qn + (tok * G + kvh) * dk + i);
                 cp_async4(ks + tt * dkp + i, kn + (tok * G + kvh) * dk + i);
-                if (DELTA) cp_async4(gs + tt * dkp + i, gg + (tok * H + h) * dk + i);
+                if (MODE == 1) cp_async4(gs + tt * dkp + i, gg + (tok * H + h) * dk + i);
             }
             for (int idx = tid; idx < n * kScanCols; idx += kScanThreads) {
                 const int tt = idx / kScanCols, c = idx - tt * kScanCols;
@@ -119,6 +123,7 @@ recurrent_scan_kernel(float* __restrict__ out, const float* __restrict__ qn, con
             }
         }
         if (DELTA && tid < n) cp_async4(bs + tid, bb + static_cast<int64_t>(t0 + tid) * H + h);
+        if (MODE == 2 && tid < n) cp_async4(g1 + tid, gg + static_cast<int64_t>(t0 + tid) * H + h);
     };
 
     if (begin < end) load(begin, 0);
@@ -135,6 +140,7 @@ recurrent_scan_kernel(float* __restrict__ out, const float* __restrict__ qn, con
         const float* gs = ks + kScanChunk * dkp;
         const float* vs = qs + kArrays * kScanChunk * dkp;
         const float* bs = vs + kScanChunk * kScanCols;
+        const float* g1 = bs + kScanChunk;
         auto token = [&](int tt) {
             const float* kq = ks + tt * dkp + part;
             const float* qq = qs + tt * dkp + part;
@@ -142,10 +148,11 @@ recurrent_scan_kernel(float* __restrict__ out, const float* __restrict__ qn, con
             float o0 = 0.f, o1 = 0.f;
             if (DELTA) {
                 const float* gq = gs + tt * dkp + part;
+                const float gh = MODE == 2 ? g1[tt] : 1.f;
                 float d0 = 0.f, d1 = 0.f;
 #pragma unroll
                 for (int r = 0; r < KPT; ++r) {
-                    S[r] *= gq[r * kScanLanes];
+                    S[r] *= MODE == 2 ? gh : gq[r * kScanLanes];
                     if (r & 1) d1 = fmaf(S[r], kq[r * kScanLanes], d1); else d0 = fmaf(S[r], kq[r * kScanLanes], d0);
                 }
                 float dot = d0 + d1;
@@ -196,7 +203,7 @@ delta_prep_kernel(float* __restrict__ qn, float* __restrict__ kn, float* __restr
                   const float* __restrict__ a, const float* __restrict__ dt_bias, const float* __restrict__ a_log,
                   const float* __restrict__ b, const float* __restrict__ state, int64_t state_floats, int64_t conv_off,
                   const int* __restrict__ seq_of_token, const int* __restrict__ cu_seqlens, const int* __restrict__ state_slots,
-                  int num_slots, int H, int G, int dk, int dv, int* __restrict__ err) {
+                  int num_slots, int H, int G, int dk, int dv, int gd, int* __restrict__ err) {
     pdl_trigger();
     pdl_wait();
     extern __shared__ float sm[];                 // conv outputs of q and k: [2 * G * dk]
@@ -236,10 +243,10 @@ delta_prep_kernel(float* __restrict__ qn, float* __restrict__ kn, float* __restr
         else dst = kn + (t * G + (grp - G)) * dk;
         for (int i = lane; i < dk; i += 32) dst[i] = x[i] * inv;
     }
-    for (int i = tid; i < H * dk; i += kPrepThreads) {
-        const float z = a[t * H * dk + i] + dt_bias[i];
+    for (int i = tid; i < H * gd; i += kPrepThreads) {          // gd decays per head: one per key channel, or one
+        const float z = a[t * H * gd + i] + dt_bias[i];
         const float sp = z > 20.f ? z : log1pf(expf(z));
-        gg[t * H * dk + i] = expf(-expf(a_log[i / dk]) * sp);
+        gg[t * H * gd + i] = expf(-expf(a_log[i / gd]) * sp);
     }
     for (int i = tid; i < H; i += kPrepThreads) bb[t * H + i] = sigmoid_of(b[t * H + i]);
 }
@@ -279,20 +286,20 @@ using namespace cvb;
         else { CALL(32); }                          \
     } while (0)
 
-template <int KPT, bool DELTA>
+template <int KPT, int MODE>
 static int launch_scan(float* out, const float* qn, const float* kn, const float* vv, const float* gg, const float* bb, const float* decay,
                        float* state, int64_t state_floats, const int* cu_seqlens, const int* state_slots, int num_slots, int S, int H, int G,
                        int dk, int dv, int* err_flag, cudaStream_t stream) {
-    constexpr int arrays = DELTA ? 3 : 2;
-    const size_t smem = static_cast<size_t>(2) * (arrays * kScanChunk * KPT * kScanLanes + kScanChunk * kScanCols + kScanChunk) * sizeof(float);
+    constexpr int arrays = MODE == 1 ? 3 : 2;
+    const size_t smem = static_cast<size_t>(2) * (arrays * kScanChunk * KPT * kScanLanes + kScanChunk * kScanCols + 2 * kScanChunk) * sizeof(float);
     static bool raised = false;
     if (smem > 48 * 1024 && !raised) {
-        if (cudaFuncSetAttribute(recurrent_scan_kernel<KPT, DELTA>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess)
+        if (cudaFuncSetAttribute(recurrent_scan_kernel<KPT, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess)
             return launch_status();
         raised = true;
     }
     const dim3 grid(S, H, (dv + kScanCols - 1) / kScanCols);
-    launch_kernel(recurrent_scan_kernel<KPT, DELTA>, grid, dim3(kScanThreads), smem, stream, out, qn, kn, vv, gg, bb, decay, state,
+    launch_kernel(recurrent_scan_kernel<KPT, MODE>, grid, dim3(kScanThreads), smem, stream, out, qn, kn, vv, gg, bb, decay, state,
                   state_floats, cu_seqlens, state_slots, num_slots, H, G, dk, dv, err_flag);
     return launch_status();
 }
@@ -321,7 +328,7 @@ extern "C" int cvb_lightning_scan(float* out, const float* qf, const float* kf, 
     if (S < 0 || H <= 0 || H > 65535 || dk <= 0 || dk > 256 || dv <= 0 || num_slots <= 0) return CVB_E_SIZE;
     if (state_floats < static_cast<int64_t>(H) * dk * dv) return CVB_E_SHAPE;
     if (!aligned16(qf) || !aligned16(kf) || !aligned16(vf)) return CVB_E_ALIGN;
-#define CALL_K(KPT) return launch_scan<KPT, false>(out, qf, kf, vf, nullptr, nullptr, decay, state, state_floats, cu_seqlens, state_slots, \
+#define CALL_K(KPT) return launch_scan<KPT, 0>(out, qf, kf, vf, nullptr, nullptr, decay, state, state_floats, cu_seqlens, state_slots, \
                                                    num_slots, S, H, H, dk, dv, err_flag, stream)
     CVB_DISPATCH_KPT(dk, CALL_K);
 #undef CALL_K
@@ -330,17 +337,18 @@ extern "C" int cvb_lightning_scan(float* out, const float* qf, const float* kf, 
 extern "C" int cvb_delta_prep(float* qn, float* kn, float* vv, float* gg, float* bb, const void* packed, int T, int stride, int qkv_off,
                               const float* conv_w, int taps, const float* a, const float* dt_bias, const float* a_log, const float* b,
                               const float* state, int64_t state_floats, int64_t conv_off, const int* seq_of_token,
-                              const int* cu_seqlens, const int* state_slots, int num_slots, int H, int G, int dk, int dv, int dtype,
-                              int* err_flag, cudaStream_t stream) {
+                              const int* cu_seqlens, const int* state_slots, int num_slots, int H, int G, int dk, int dv, int gd,
+                              int dtype, int* err_flag, cudaStream_t stream) {
     if (T == 0) return CVB_OK;
     if (T < 0 || H <= 0 || G <= 0 || dk <= 0 || dv <= 0 || taps <= 0 || num_slots <= 0) return CVB_E_SIZE;
     const int64_t C = 2LL * G * dk + static_cast<int64_t>(H) * dv;
     if (H % G || qkv_off < 0 || stride < qkv_off + C || state_floats < conv_off + (taps - 1) * C) return CVB_E_SHAPE;
+    if (gd != dk && gd != 1) return CVB_E_SHAPE;
     const size_t smem = static_cast<size_t>(2) * G * dk * sizeof(float);
     if (smem > 48 * 1024) return CVB_E_SIZE;
 #define CALL(TY) launch_kernel(delta_prep_kernel<TY>, dim3(T), dim3(kPrepThreads), smem, stream, qn, kn, vv, gg, bb, (const TY*)packed, \
                                stride, qkv_off, conv_w, taps, a, dt_bias, a_log, b, state, state_floats, conv_off, seq_of_token,       \
-                               cu_seqlens, state_slots, num_slots, H, G, dk, dv, err_flag)
+                               cu_seqlens, state_slots, num_slots, H, G, dk, dv, gd, err_flag)
     CVB_DISPATCH_DTYPE(dtype, CALL);
 #undef CALL
     return launch_status();
@@ -362,13 +370,19 @@ extern "C" int cvb_conv_history(float* state, int64_t state_floats, int64_t conv
 
 extern "C" int cvb_delta_scan(float* out, const float* qn, const float* kn, const float* vv, const float* gg, const float* bb,
                               float* state, int64_t state_floats, const int* cu_seqlens, const int* state_slots, int num_slots, int S,
-                              int H, int G, int dk, int dv, int* err_flag, cudaStream_t stream) {
+                              int H, int G, int dk, int dv, int gd, int* err_flag, cudaStream_t stream) {
     if (S == 0) return CVB_OK;
     if (S < 0 || H <= 0 || H > 65535 || G <= 0 || dk <= 0 || dk > 256 || dv <= 0 || num_slots <= 0) return CVB_E_SIZE;
-    if (H % G || state_floats < static_cast<int64_t>(H) * dk * dv) return CVB_E_SHAPE;
+    if (H % G || state_floats < static_cast<int64_t>(H) * dk * dv || (gd != dk && gd != 1)) return CVB_E_SHAPE;
     if (!aligned16(qn) || !aligned16(kn) || !aligned16(vv) || !aligned16(gg)) return CVB_E_ALIGN;
-#define CALL_K(KPT) return launch_scan<KPT, true>(out, qn, kn, vv, gg, bb, nullptr, state, state_floats, cu_seqlens, state_slots, num_slots, \
-                                                  S, H, G, dk, dv, err_flag, stream)
+    if (gd == 1 && dk != 1) {
+#define CALL_K(KPT) return launch_scan<KPT, 2>(out, qn, kn, vv, gg, bb, nullptr, state, state_floats, cu_seqlens, state_slots, num_slots, \
+                                               S, H, G, dk, dv, err_flag, stream)
+        CVB_DISPATCH_KPT(dk, CALL_K);
+#undef CALL_K
+    }
+#define CALL_K(KPT) return launch_scan<KPT, 1>(out, qn, kn, vv, gg, bb, nullptr, state, state_floats, cu_seqlens, state_slots, num_slots, \
+                                               S, H, G, dk, dv, err_flag, stream)
     CVB_DISPATCH_KPT(dk, CALL_K);
 #undef CALL_K
 }

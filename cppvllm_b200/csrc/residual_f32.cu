@@ -14,6 +14,7 @@
 //                     new stream in the activations' type is written beside it (what the next sublayer's products read).
 //   bias_act        : out = T( act(x + b) ), act = identity | relu(z)^2 | tanh-GELU
 //   gated_norm      : out[t, g, j] = T( o / sqrt(mean_j(o[t, g, :]^2) + eps) * w[j] * sigmoid(gate[t, g, j]) ) over groups of
+//                     (or times silu(gate): `gate_act` = 1) over groups of
 //                     equal size (one group: a norm over the whole row; one group per head: a norm per head with a weight
 //                     that the heads share); o is float, the gate a column range of a packed projection
 //
@@ -288,7 +289,7 @@ __global__ void bias_act_bf16x8_kernel(__nv_bfloat16* __restrict__ out, const __
 template <typename T>
 __global__ void __launch_bounds__(kUpdateThreads)
 gated_norm_block_kernel(T* __restrict__ out, const float* __restrict__ o, const T* __restrict__ gate, int gate_stride,
-                        const float* __restrict__ w, int groups, int G, float eps) {
+                        const float* __restrict__ w, int groups, int G, float eps, int gate_act) {
     pdl_trigger();
     pdl_wait();
     __shared__ float scratch[32];
@@ -301,7 +302,7 @@ gated_norm_block_kernel(T* __restrict__ out, const float* __restrict__ o, const 
     const float inv = 1.f / sqrtf(ss / static_cast<float>(G) + eps);
     for (int j = threadIdx.x; j < G; j += kUpdateThreads) {
         const float z = to_float(gate[row * gate_stride + g * G + j]);
-        out[(row * groups + g) * G + j] = from_float<T>(og[j] * inv * w[j] * (1.f / (1.f + expf(-z))));
+        out[(row * groups + g) * G + j] = from_float<T>(og[j] * inv * w[j] * (gate_act ? z : 1.f) * (1.f / (1.f + expf(-z))));
     }
 }
 
@@ -309,7 +310,7 @@ gated_norm_block_kernel(T* __restrict__ out, const float* __restrict__ o, const 
 template <typename T>
 __global__ void __launch_bounds__(kUpdateThreads)
 gated_norm_kernel(T* __restrict__ out, const float* __restrict__ o, const T* __restrict__ gate, int gate_stride,
-                  const float* __restrict__ w, int groups, int G, float eps) {
+                  const float* __restrict__ w, int groups, int G, float eps, int gate_act) {
     pdl_trigger();
     pdl_wait();
     const int64_t row = blockIdx.x;
@@ -322,7 +323,7 @@ gated_norm_kernel(T* __restrict__ out, const float* __restrict__ o, const T* __r
         const float inv = 1.f / sqrtf(ss / static_cast<float>(G) + eps);
         for (int j = lane; j < G; j += 32) {
             const float z = to_float(gate[row * gate_stride + g * G + j]);
-            out[(row * groups + g) * G + j] = from_float<T>(og[j] * inv * w[j] * (1.f / (1.f + expf(-z))));
+            out[(row * groups + g) * G + j] = from_float<T>(og[j] * inv * w[j] * (gate_act ? z : 1.f) * (1.f / (1.f + expf(-z))));
         }
     }
 }
@@ -447,17 +448,17 @@ extern "C" int cvb_bias_act(void* out, const void* x, const float* bias, int64_t
 }
 
 extern "C" int cvb_gated_norm(void* out, const float* o, const void* gate, int gate_stride, const float* w, int T, int groups, int G,
-                              float eps, int dtype, cudaStream_t stream) {
+                              float eps, int gate_act, int dtype, cudaStream_t stream) {
     if (T == 0) return CVB_OK;
-    if (T < 0 || groups <= 0 || G <= 0) return CVB_E_SIZE;
+    if (T < 0 || groups <= 0 || G <= 0 || gate_act < 0 || gate_act > 1) return CVB_E_SIZE;
     if (gate_stride < groups * G) return CVB_E_SHAPE;
     if (groups > 65535) return CVB_E_SIZE;
     const int per_block = kUpdateThreads / 32;
 #define CALL(TY)                                                                                                                 \
     if (G > 256) launch_kernel(gated_norm_block_kernel<TY>, dim3(T, groups), dim3(kUpdateThreads), 0, stream, (TY*)out, o,       \
-                               (const TY*)gate, gate_stride, w, groups, G, eps);                                                 \
+                               (const TY*)gate, gate_stride, w, groups, G, eps, gate_act);                                                 \
     else launch_kernel(gated_norm_kernel<TY>, dim3(T, (groups + per_block - 1) / per_block), dim3(kUpdateThreads), 0, stream,    \
-                       (TY*)out, o, (const TY*)gate, gate_stride, w, groups, G, eps)
+                       (TY*)out, o, (const TY*)gate, gate_stride, w, groups, G, eps, gate_act)
     CVB_DISPATCH_DTYPE(dtype, CALL);
 #undef CALL
     return launch_status();

@@ -61,8 +61,14 @@ class CausalLM:
         return units
 
     def state_specs(self) -> List[Optional[StateSpec]]:
-        """One entry per item of the run list: the fixed-size per-request state its mixer wants, or None."""
-        return [self.blocks[e.layer].mixer.state_spec() for e in self.run_order]
+        """One entry per item of the run list: the fixed-size per-request state its mixer wants, or None.  A block that keeps
+        state of its own (``state_spec()`` on the block) answers for its mixer too."""
+        out = []
+        for e in self.run_order:
+            b = self.blocks[e.layer]
+            own = getattr(b, "state_spec", None)
+            out.append(own() if own is not None else b.mixer.state_spec())
+        return out
 
     def _check_shared_caches(self) -> None:
         units = self.cache_units()
@@ -121,9 +127,18 @@ class CausalLM:
         else:
             h = embedded = self.embedding.forward(ctx.tokens, ctx.num_tokens)
         pending = None
+        last = len(self.run_order) - 1
         for i, e in enumerate(self.run_order):
             if e.input is not None:
                 h, pending = self.inputs[e.input].forward(h, pending, embedded, e.input_index)
+            # the norm that reads the stream next: a block that holds the new row on the chip may apply it ahead of time
+            if i == last:
+                ctx.extras["norm_ahead"] = self.final_norm
+            else:
+                nxt = self.run_order[i + 1]
+                nb = self.blocks[nxt.layer]
+                takes = nxt.input is None and getattr(nb, "accepts_normed_ahead", False)
+                ctx.extras["norm_ahead"] = nb.mixer_norm if takes else None
             h, pending = self.blocks[e.layer].forward(h, pending, ctx, caches.get(i), states.get(i))
         return h, pending
 
@@ -131,8 +146,11 @@ class CausalLM:
         h, pending = self.forward_hidden(ctx, caches, states)
         R = ctx.num_logit_rows
         ws = self.rt.workspace
-        rows_h = ops.gather_rows(ws.rows("head_rows", R, self.hidden_size, h.dtype), h, ctx.logit_rows)
         normed = ws.rows("head_normed", R, self.hidden_size, self.rt.dtype)
+        if getattr(pending, "weight", None) is not None and pending.weight is getattr(self.final_norm, "weight", None):
+            # the last block has applied the final norm already: only the wanted rows are picked
+            return self.head.forward(ops.gather_rows(normed, pending.rows, ctx.logit_rows), logits_out[:R])
+        rows_h = ops.gather_rows(ws.rows("head_rows", R, self.hidden_size, h.dtype), h, ctx.logit_rows)
         if isinstance(pending, tuple):               # several deltas (a block whose sublayers run side by side)
             rows_p = tuple(ops.gather_rows(ws.rows(f"head_pending{i}", R, self.hidden_size, p.dtype), p, ctx.logit_rows)
                            for i, p in enumerate(pending))

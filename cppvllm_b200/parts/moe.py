@@ -10,6 +10,12 @@
   experts' weights pair by pair (two kernels spread over all SMs); more are sorted by expert on the device and go through
   two grouped products on the tcgen05 kernel (csrc/moe.cu, csrc/gemm_tcgen05.cu); nothing travels to the host, so steps
   stay capturable.
+* ``clamped_glu``: dense and gated with clamps: g = min(Wgate x, L), u = clamp(Wup x, -L, L); y = Wdown (g sigmoid(alpha g) (u + 1)).
+* ``routed_act``: a mixture of ungated experts Wdown act(Wup x) (act = relu2) whose weights are `scale` times the chosen experts'
+  shares of the softmax over ALL experts (not renormalised over the winners); no router bias.  Optionally a shared expert of
+  the same form and a size of its own runs for every token and joins through sigmoid(w_sg . x), one number per token; its
+  gate's row rides behind the router's rows, so one kernel makes both.  Same kernels as ``routed_glu`` with the activation
+  as a parameter (the grouped tcgen05 product takes the squared relu as its epilogue).
 """
 from __future__ import annotations
 
@@ -115,3 +121,109 @@ class RoutedGLU(FeedForward):
         y = ws.rows("ffn_out", T, self.hidden_size, x.dtype)
         return ops.routed_experts(y, x, ids, weights, self.w_gate_up, self.w_down, workspace=ws,
                                   kernel="rows" if self.rt.plain_kernels else "")
+
+
+@register_part("ffn", "clamped_glu")
+class ClampedGLU(FeedForward):
+    def __init__(self, runtime, prefix="", names=None, *, hidden_size: int, intermediate_size: int, limit: float, alpha: float = 1.702,
+                 gate_name: str = "gate", up_name: str = "up", down_name: str = "down"):
+        super().__init__(runtime, prefix, names)
+        self.hidden_size, self.intermediate_size = int(hidden_size), int(intermediate_size)
+        self.limit, self.alpha = float(limit), float(alpha)
+        self.gate_name, self.up_name, self.down_name = gate_name, up_name, down_name
+        self.w_gate_up = self.w_down = None
+
+    def weight_specs(self) -> Dict[str, WeightSpec]:
+        D, I = self.hidden_size, self.intermediate_size
+        return {self.full_name(self.gate_name): WeightSpec((I, D)), self.full_name(self.up_name): WeightSpec((I, D)),
+                self.full_name(self.down_name): WeightSpec((D, I))}
+
+    def bind(self, tensors) -> None:
+        g, u = tensors[self.full_name(self.gate_name)], tensors[self.full_name(self.up_name)]
+        if g.dtype != u.dtype:
+            g, u = g.float(), u.float()
+        self.w_gate_up = torch.cat([g, u], dim=0).contiguous()
+        self.w_down = tensors[self.full_name(self.down_name)]
+
+    def weight_bytes(self) -> int:
+        return sum(w.numel() * w.element_size() for w in (self.w_gate_up, self.w_down))
+
+    def _project(self, x, w, out, rows):
+        return ops.linear(x, w, out=out) if self.rt.plain_kernels else ops.project_rows(x, w, out, rows)
+
+    def forward(self, x, ctx):
+        T = x.shape[0]
+        ws = self.rt.workspace
+        gu = self._project(x, self.w_gate_up, ws.rows("ffn_gate_up", T, 2 * self.intermediate_size, x.dtype), T)
+        act = ops.glu_clamped(ws.rows("ffn_act", T, self.intermediate_size, x.dtype), gu, self.limit, self.alpha)
+        return self._project(act, self.w_down, ws.rows("ffn_out", T, self.hidden_size, x.dtype), T)
+
+
+@register_part("ffn", "routed_act")
+class RoutedAct(FeedForward):
+    def __init__(self, runtime, prefix="", names=None, *, hidden_size: int, intermediate_size: int, num_experts: int, top: int,
+                 scale: float = 1.0, activation: str = "relu2", shared_size: int = 0, router_name: str = "router",
+                 expert_prefix: str = "e", shared_prefix: str = "shared."):
+        super().__init__(runtime, prefix, names)
+        if activation != "relu2":
+            raise ValueError(f"activation '{activation}' is not built for ungated experts; built: relu2")
+        self.hidden_size, self.intermediate_size = int(hidden_size), int(intermediate_size)
+        self.num_experts, self.top, self.scale = int(num_experts), int(top), float(scale)
+        if not (0 < self.top <= self.num_experts):
+            raise ValueError(f"a token cannot use {self.top} of {self.num_experts} experts")
+        self.shared_size = int(shared_size)
+        self.router_name, self.expert_prefix, self.shared_prefix = router_name, expert_prefix, shared_prefix
+        self.w_router = self.w_up = self.w_down = self.shared_up = self.shared_down = None
+
+    def _expert(self, e: int, which: str) -> str:
+        return self.full_name(f"{self.expert_prefix}{e}.{which}")
+
+    def weight_specs(self) -> Dict[str, WeightSpec]:
+        D, I, E = self.hidden_size, self.intermediate_size, self.num_experts
+        specs = {self.full_name(self.router_name): WeightSpec((E, D), role="vector")}
+        for e in range(E):
+            specs[self._expert(e, "up")] = WeightSpec((I, D))
+            specs[self._expert(e, "down")] = WeightSpec((D, I))
+        if self.shared_size:
+            sp = self.shared_prefix
+            specs[self.full_name(sp + "up")] = WeightSpec((self.shared_size, D))
+            specs[self.full_name(sp + "down")] = WeightSpec((D, self.shared_size))
+            specs[self.full_name(sp + "sg")] = WeightSpec((1, D), role="vector")
+        return specs
+
+    def bind(self, tensors) -> None:
+        E = self.num_experts
+        router = tensors[self.full_name(self.router_name)]
+        self.w_up = torch.stack([tensors[self._expert(e, "up")] for e in range(E)], dim=0).to(self.rt.dtype).contiguous()
+        self.w_down = torch.stack([tensors[self._expert(e, "down")] for e in range(E)], dim=0).to(self.rt.dtype).contiguous()
+        if self.shared_size:
+            sp = self.shared_prefix
+            router = torch.cat([router, tensors[self.full_name(sp + "sg")].reshape(1, -1)], dim=0)
+            self.shared_up, self.shared_down = tensors[self.full_name(sp + "up")], tensors[self.full_name(sp + "down")]
+        self.w_router = router.contiguous()
+
+    def weight_bytes(self) -> int:
+        """What a decoded token reads: the router, `top` of the experts and the shared expert."""
+        per_expert = (self.w_up.numel() + self.w_down.numel()) * self.w_down.element_size() // self.num_experts
+        shared = sum(w.numel() * w.element_size() for w in (self.shared_up, self.shared_down)) if self.shared_size else 0
+        return self.w_router.numel() * 4 + self.top * per_expert + shared
+
+    def _project(self, x, w, out, rows):
+        return ops.linear(x, w, out=out) if self.rt.plain_kernels else ops.project_rows(x, w, out, rows)
+
+    def forward(self, x, ctx):
+        T = x.shape[0]
+        ws = self.rt.workspace
+        ids = ws.rows("moe_ids", T, self.top, torch.int32)
+        weights = ws.rows("moe_weights", T, self.top, torch.float32)
+        gate = ws.rows("moe_shared_gate", T, 1, torch.float32) if self.shared_size else None
+        ops.route_topk(ids, weights, x, self.w_router, None, over_all=True, scale=self.scale, extra_out=gate)
+        y = ws.rows("ffn_out", T, self.hidden_size, x.dtype)
+        ops.routed_experts(y, x, ids, weights, self.w_up, self.w_down, workspace=ws, kernel="rows" if self.rt.plain_kernels else "",
+                           gated=False)
+        if self.shared_size:
+            up = self._project(x, self.shared_up, ws.rows("ffn_up", T, self.shared_size, x.dtype), T)
+            ops.bias_act(up, up, None, "relu2")
+            s = self._project(up, self.shared_down, ws.rows("ffn_shared", T, self.hidden_size, x.dtype), T)
+            ops.add_gated_rows(y, s, gate.view(-1))
+        return y

@@ -11,6 +11,9 @@ type; only the projections around them are products in the activations' type.
   h / (heads / kv_heads));  y = Wo concat_h(RMSNorm(o_h) * w * sigmoid(Wg2 Wg1 x)_h), w shared by the heads.  State per request:
   [H, dim, vdim] and behind it the last taps - 1 inputs of the convolutions [taps - 1, channels].  The inner sizes of the
   two low-rank projections are whatever the checkpoint holds.
+* ``head_delta``: the same rule with ONE decay per head and token, g = exp(-exp(A_h) * softplus(Wa x + dt_h)), S <- g S, full-rank
+  projections for the decay (Wa [H, D]) and the output gate (Wg [H * vdim, D]), and the gate through silu instead of the
+  logistic function: y = Wo concat_h(RMSNorm(o_h) * w * silu(Wg x)_h).
 """
 from __future__ import annotations
 
@@ -145,4 +148,65 @@ class ChannelDeltaMixer(Mixer):
         o = ws.rows("rec_o", T, H * dv, f32)
         ops.delta_scan(o, qn, kn, vv, gg, bb, state, ctx.cu_seqlens, ctx.state_slots, S, H, G, dk, dv)
         y = ops.gated_norm(ws.rows("rec_y", T, H * dv, x.dtype), o, gate, self.w_norm, H, self.eps)
+        return _project(self.rt, y, self.w_o, ws.rows("attn_proj", T, self.hidden_size, x.dtype), T)
+
+
+@register_part("mixer", "head_delta")
+class HeadDeltaMixer(Mixer):
+    def __init__(self, runtime, prefix="", names=None, *, hidden_size: int, num_heads: int, num_kv_heads: int, dim: int, vdim: int,
+                 taps: int, eps: float):
+        super().__init__(runtime, prefix, names)
+        self.hidden_size, self.num_heads, self.num_kv_heads = int(hidden_size), int(num_heads), int(num_kv_heads)
+        self.dim, self.vdim, self.taps, self.eps = int(dim), int(vdim), int(taps), float(eps)
+        if self.num_heads % self.num_kv_heads:
+            raise ValueError(f"{self.num_heads} heads are not a multiple of {self.num_kv_heads} query/key heads")
+        if self.taps < 1:
+            raise ValueError("a convolution has at least one tap")
+        if self.dim > 256:
+            raise ValueError("the scan kernel keeps at most 256 key channels per head")
+        self.channels = 2 * self.num_kv_heads * self.dim + self.num_heads * self.vdim
+        self.matrix_floats = self.num_heads * self.dim * self.vdim
+
+    def state_spec(self) -> StateSpec:
+        return StateSpec((self.matrix_floats + (self.taps - 1) * self.channels,), torch.float32)
+
+    def weight_specs(self) -> Dict[str, WeightSpec]:
+        D, H, G, dk, dv, K = self.hidden_size, self.num_heads, self.num_kv_heads, self.dim, self.vdim, self.taps
+        f = self.full_name
+        return {f("q"): WeightSpec((G * dk, D)), f("q.conv"): WeightSpec((G * dk, K), role="vector"),
+                f("k"): WeightSpec((G * dk, D)), f("k.conv"): WeightSpec((G * dk, K), role="vector"),
+                f("v"): WeightSpec((H * dv, D)), f("v.conv"): WeightSpec((H * dv, K), role="vector"),
+                f("b"): WeightSpec((H, D)), f("a"): WeightSpec((H, D)), f("A_log"): WeightSpec((H,), role="vector"),
+                f("dt_bias"): WeightSpec((H,), role="vector"), f("norm"): WeightSpec((dv,), role="vector", init="norm"),
+                f("g"): WeightSpec((H * dv, D)), f("o"): WeightSpec((D, H * dv))}
+
+    def bind(self, tensors) -> None:
+        t = lambda n: tensors[self.full_name(n)]          # noqa: E731
+        self.w_in = _cat_rows([t("q"), t("k"), t("v"), t("g")])
+        self.g_off = self.channels
+        self.w_b, self.w_a, self.w_o = t("b"), t("a"), t("o")
+        self.conv_w = torch.cat([t("q.conv"), t("k.conv"), t("v.conv")], dim=0).contiguous()
+        self.dt_bias, self.a_log, self.w_norm = t("dt_bias"), t("A_log"), t("norm")
+
+    def weight_bytes(self) -> int:
+        return sum(w.numel() * w.element_size() for w in (self.w_in, self.w_b, self.w_a, self.w_o))
+
+    def forward(self, x, ctx, cache, state):
+        T, S = x.shape[0], ctx.num_seqs
+        H, G, dk, dv = self.num_heads, self.num_kv_heads, self.dim, self.vdim
+        ws = self.rt.workspace
+        f32 = torch.float32
+        packed = _project(self.rt, x, self.w_in, ws.rows("rec_in", T, self.w_in.shape[0], x.dtype), T)
+        # what enters the recurrence leaves its product unrounded
+        b = ops.linear(x, self.w_b, out=ws.rows("delta_b", T, H, f32), out_dtype=f32)
+        a = ops.linear(x, self.w_a, out=ws.rows("delta_a1", T, H, f32), out_dtype=f32)
+        qn, kn = ws.rows("delta_q", T, G * dk, f32), ws.rows("delta_k", T, G * dk, f32)
+        vv, gg, bb = ws.rows("delta_v", T, H * dv, f32), ws.rows("delta_g1", T, H, f32), ws.rows("delta_beta", T, H, f32)
+        ops.delta_prep(qn, kn, vv, gg, bb, packed, 0, self.conv_w, a, self.dt_bias, self.a_log, b, state, self.matrix_floats,
+                       ctx.seq_of_token, ctx.cu_seqlens, ctx.state_slots, H, G, dk, dv, decay_dim=1)
+        ops.conv_history(state, self.matrix_floats, packed, 0, self.channels, self.taps, ctx.cu_seqlens, ctx.state_slots, S)
+        o = ws.rows("rec_o", T, H * dv, f32)
+        ops.delta_scan(o, qn, kn, vv, gg, bb, state, ctx.cu_seqlens, ctx.state_slots, S, H, G, dk, dv, decay_dim=1)
+        y = ops.gated_norm(ws.rows("rec_y", T, H * dv, x.dtype), o, packed[:, self.g_off:self.g_off + H * dv], self.w_norm, H, self.eps,
+                           gate_act="silu")
         return _project(self.rt, y, self.w_o, ws.rows("attn_proj", T, self.hidden_size, x.dtype), T)

@@ -84,6 +84,8 @@ class ScaledPositionEmbedding(Part):
 
 @register_part("norm", "rmsnorm_wide")
 class WideRMSNorm(Norm):
+    plain_rms = True          # y = x / rms(x) * self.weight with self.eps: a kernel that holds the row may apply it ahead of time
+
     def __init__(self, runtime, prefix="", names=None, *, size: int, eps: float, buffer: str = "normed",
                  weight_name: str = "weight", offset: float = 0.0):
         super().__init__(runtime, prefix, names)
