@@ -39,6 +39,7 @@ LIBRARIES: Dict[str, List[str]] = {
     "attn_tcgen05": ["attention_tcgen05.cu"],
     "resid32": ["residual_f32.cu"],
     "attn_keys": ["attention_keys.cu"],
+    "attn_bias": ["attention_bias.cu"],
     "moe": ["moe.cu"],
     "latent": ["latent.cu"],
     "recurrent": ["recurrent.cu"],
@@ -47,7 +48,7 @@ LIBRARIES: Dict[str, List[str]] = {
     "runtime": ["cache_runtime.cpp", "scheduler_runtime.cpp"],
 }
 
-_HEADERS = ["common.cuh", "sm100.cuh", "tensor_map.cuh", "attention_bf16.h", "runtime.hpp"]
+_HEADERS = ["common.cuh", "sm100.cuh", "tensor_map.cuh", "mma_tiles.cuh", "attention_bf16.h", "runtime.hpp"]
 _loaded: Dict[str, ctypes.CDLL] = {}
 _lock = threading.Lock()
 

@@ -448,9 +448,51 @@ def wide_qk_prep(q_out: torch.Tensor, packed: torch.Tensor, q_weight: torch.Tens
     return q_out
 
 
+_attn_bias = None
+
+
+def _attn_bias_lib():
+    global _attn_bias
+    if _attn_bias is None:
+        lib = load_library("attn_bias")
+        lib.cvb_attn_bias_bf16.restype = c_int
+        _attn_bias = lib
+    return _attn_bias
+
+
 def attn_bias_supported(dtype: torch.dtype, num_heads: int, num_kv_heads: int, dim: int, vdim: int) -> bool:
-    """Whether the tensor-core kernel takes the shape (csrc/attention_bias.cu)."""
-    return False
+    """Whether the tensor-core kernel takes the shape (csrc/attention_bias.cu): bf16, key and value sizes 16 to 128 in steps
+    of 16, up to 64 query heads per kv head."""
+    return (dtype == torch.bfloat16 and dim % 16 == 0 and 16 <= dim <= 128 and vdim % 16 == 0 and 16 <= vdim <= 128
+            and num_kv_heads > 0 and num_heads % num_kv_heads == 0 and num_heads // num_kv_heads <= 64)
+
+
+def attn_bias_bf16(out: torch.Tensor, q: torch.Tensor, pages: torch.Tensor, block_tables: torch.Tensor, cu_seqlens: torch.Tensor,
+                   positions: torch.Tensor, num_seqs: int, num_tiles: int, num_heads: int, num_kv_heads: int, dim: int, vdim: int,
+                   page_size: int, scale: float, bias: torch.Tensor, all_single: bool = False, splits: int = 1,
+                   scratch: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Attention of prompt portions and decoded tokens over pages [kv head, slot, dim + vdim] whose entries hold a key and,
+    behind it, its value; the score of key j for the token at position p receives bias[h, min(p - j, L - 1)] (float32 [H, L])
+    after the scale.  `num_tiles` as attn_keys_tiles gives it.  `all_single`: every request brings exactly one token; with
+    `splits` > 1 that many blocks share a (request, kv head), through `scratch` (float32, attn_keys_scratch_floats with vdim
+    as the head size) and a merge kernel."""
+    _cuda(out, q, pages, block_tables, cu_seqlens, positions, bias); _contig(out, q, pages, block_tables, cu_seqlens, positions, bias)
+    if q.dtype != torch.bfloat16 or pages.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
+        raise KernelError("attn_bias_bf16 takes bf16 queries, pages and output")
+    if block_tables.dtype != torch.int32 or block_tables.dim() != 2 or cu_seqlens.dtype != torch.int32 or positions.dtype != torch.int32:
+        raise KernelError("attn_bias_bf16: block_tables [S, W], cu_seqlens and positions must be int32")
+    if bias.dtype != torch.float32 or bias.dim() != 2 or bias.shape[0] != num_heads:
+        raise KernelError("attn_bias_bf16: bias is float32 [H, L]")
+    num_pages = pages.numel() // (num_kv_heads * page_size * (dim + vdim))
+    if splits > 1 and (scratch is None or scratch.dtype != torch.float32 or not scratch.is_cuda or not scratch.is_contiguous()):
+        raise KernelError("attn_bias_bf16: splits need a contiguous float32 CUDA scratch")
+    _check(_attn_bias_lib().cvb_attn_bias_bf16(
+        _ptr(out), _ptr(q), c_int(q.shape[1]), _ptr(pages), _ptr(block_tables), c_int(block_tables.shape[1]), _ptr(cu_seqlens),
+        _ptr(positions), c_int(num_seqs), c_int(num_tiles), c_int(num_heads), c_int(num_kv_heads), c_int(dim), c_int(vdim),
+        c_int(page_size), c_float(scale), _ptr(bias), c_int(bias.shape[1]), c_int(num_pages), c_int(1 if all_single else 0),
+        c_int(splits), _ptr(scratch), c_int64(scratch.numel() if scratch is not None else 0),
+        _ptr(error_flag(q.device)), _stream()), "attn_bias_bf16", kernels=2 if all_single and splits > 1 else 1)
+    return out
 
 
 def paged_attention_entries(out: torch.Tensor, q: torch.Tensor, pages: torch.Tensor, block_tables: torch.Tensor,

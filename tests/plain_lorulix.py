@@ -203,9 +203,14 @@ def relu2_expert(h, up, down, rnd):
     return rnd(rnd(torch.relu(rnd(h @ up.T)) ** 2) @ down.T)
 
 
-def routed_experts(h, w, pre, f, rnd):
+def routed_experts(h, w, pre, f, rnd, margins=None):
+    """`margins` (a list) receives, per token, how far the last chosen expert's logit lies above the first one left out."""
     E, top, scale = f["router"]["experts"], f["router"]["top"], f["router"]["scale"]
-    s = torch.softmax(h @ w[pre + "router"].T, dim=-1)
+    z = h @ w[pre + "router"].T
+    if margins is not None:
+        ranked = torch.sort(z, dim=-1, descending=True).values
+        margins.append(ranked[:, top - 1] - ranked[:, top] if top < E else torch.full((h.shape[0],), math.inf, dtype=F))
+    s = torch.softmax(z, dim=-1)
     chosen = torch.topk(s, top, dim=-1).indices
     y = torch.zeros(h.shape[0], w[pre + "e0.down"].shape[0], dtype=F)
     for e in range(E):
@@ -219,8 +224,9 @@ def routed_experts(h, w, pre, f, rnd):
 
 # ---- the model ---------------------------------------------------------------------------------------------------------
 
-def forward(cfg: dict, w: dict, tokens, rnd=identity, layer_outputs=None) -> torch.Tensor:
-    """Logits [T, vocab] of one whole sequence; `layer_outputs` (a list) receives the stream after every layer."""
+def forward(cfg: dict, w: dict, tokens, rnd=identity, layer_outputs=None, router_margins=None) -> torch.Tensor:
+    """Logits [T, vocab] of one whole sequence; `layer_outputs` (a list) receives the stream after every layer,
+    `router_margins` (a list) one tensor [T] per routed feed-forward (see routed_experts)."""
     eps = cfg["norm"]["eps"]
     T = len(tokens)
     x = w["embed"][torch.tensor(tokens)] + w["pos"][:T]
@@ -244,7 +250,7 @@ def forward(cfg: dict, w: dict, tokens, rnd=identity, layer_outputs=None) -> tor
         if f is not None:
             a = rnd(norm_around_zero(x, w[p + "norm2"], eps))
             h = rnd(with_input_conv(a, w[p + "canon2"]))
-            y = clamped_glu(h, w, p + "mlp.", f, rnd) if f["kind"] == "dense" else routed_experts(h, w, p + "mlp.", f, rnd)
+            y = clamped_glu(h, w, p + "mlp.", f, rnd) if f["kind"] == "dense" else routed_experts(h, w, p + "mlp.", f, rnd, router_margins)
             y = y * logistic(rnd(a @ w[p + "rg2"].T) + w[p + "rg2.b"])
             x = x + norm_around_zero(y, w[p + "norm2b"], eps)
         if layer_outputs is not None:
