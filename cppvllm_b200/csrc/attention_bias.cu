@@ -43,6 +43,13 @@ struct BiasAttnParams {
     int* err;
 };
 
+// floats per row of a block's table of biases: tok_per_tile + 63 distances and one more for the odd parity, even, and
+// = 4 mod 16 so that the rows of neighbouring heads fall on different banks
+__host__ __device__ __forceinline__ int bias_row_floats(int tok_per_tile) {
+    const int need = tok_per_tile + kBiasTileKeys;
+    return need + ((4 - need % 16) + 16) % 16;
+}
+
 __device__ __forceinline__ void bias_page_of(const BiasAttnParams& p, int j, int& slot, int& off) {
     if (p.page_shift >= 0) { slot = j >> p.page_shift; off = j & (p.page_size - 1); }
     else { slot = j / p.page_size; off = j - slot * p.page_size; }
@@ -59,9 +66,11 @@ attn_bias_kernel(const BiasAttnParams p) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     __nv_bfloat16* sQ = reinterpret_cast<__nv_bfloat16*>(smem_raw);
     __nv_bfloat16* sK = sQ + kBiasTileRows * LDQ;         // two stages of kBiasTileKeys * LD
+    float* sB = reinterpret_cast<float*>(sK + 2 * kBiasTileKeys * LD);   // the tile's biases: [g][2][XS], see stage_bias
 
     const int g = p.H / p.G;
     const int tok_per_tile = kBiasTileRows / g;
+    const int XS = bias_row_floats(tok_per_tile);
     const int kvh = blockIdx.y;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
 
@@ -90,12 +99,16 @@ attn_bias_kernel(const BiasAttnParams p) {
         cp_async16(sQ + r * LDQ + c * 8, src, valid);
     }
 
+    // a thread's chunks of a tile: chunk i = threadIdx.x + n * kBiasThreads is row i / CE, column i % CE, kept by increments
+    const int ld_r0 = threadIdx.x / CE, ld_c0 = threadIdx.x - ld_r0 * CE;
+    const int ld_dr = kBiasThreads / CE, ld_dc = kBiasThreads - ld_dr * CE;
     auto load_tile = [&](int it, int stage) {
         const int key0 = it * kBiasTileKeys;
         __nv_bfloat16* dst = sK + stage * kBiasTileKeys * LD;
         int last_slot = -1, page = -1;                    // a thread's rows ascend: the block table is read once per page
-        for (int i = threadIdx.x; i < kBiasTileKeys * CE; i += kBiasThreads) {
-            const int r = i / CE, c = i - r * CE;
+        int r = ld_r0, c = ld_c0;
+        for (; r < kBiasTileKeys; r += ld_dr, c += ld_dc) {
+            if (c >= CE) { c -= CE; ++r; if (r >= kBiasTileKeys) break; }
             const int j = key0 + r;
             bool need = j <= key_hi;
             const __nv_bfloat16* src = p.pages;
@@ -118,20 +131,34 @@ attn_bias_kernel(const BiasAttnParams p) {
     cp_async_commit();
 
     // the two rows this thread owns in its warp's slab of 16: their positions and their heads' rows of the bias table
-    int row_hi[2];
-    const float* brow[2];
+    // and where they read the tile's biases: the pair of neighbouring keys (j, j + 1) of score tile nt at tb[half][nt * 4]
+    const float2* tb[2];
     float bfar[2];
 #pragma unroll
     for (int half = 0; half < 2; ++half) {
         const int r = warp * 16 + (lane >> 2) + half * 8;
-        const int tok = min(r / g, n_tok - 1);            // rows past the block's tokens repeat the last one; never stored
-        row_hi[half] = pos_first + tok;
-        brow[half] = p.bias + static_cast<int64_t>(kvh * g + r % g) * p.L;
-        bfar[half] = brow[half][p.L - 1] * kLog2eBias;
+        const int tok = min(r / g, tok_per_tile - 1);     // rows past the block's tokens are never stored
+        const int a = tok_per_tile - 1 - tok;
+        tb[half] = reinterpret_cast<const float2*>(sB + ((r % g) * 2 + (a & 1)) * XS + (a & ~1) + ((lane & 3) << 1));
+        bfar[half] = p.bias[static_cast<int64_t>(kvh * g + r % g) * p.L + p.L - 1] * kLog2eBias;
     }
     const bool warp_has_rows = warp * 16 < n_tok * g;
     const int warp_last_pos = pos_first + min(n_tok - 1, (warp * 16 + 15) / g);
-    const int warp_first_pos = pos_first + min(n_tok - 1, (warp * 16) / g);
+    // The biases of a tile, by distance, once per block: row (head h, parity par) holds at y the bias of x = y + par, which
+    // stands for the distance d = (pos_first + tok_per_tile - 1 - key0) - x: bias[h][min(d, L - 1)] * log2(e), or -inf where
+    // d < 0 (the key lies behind the token), so that adding it is the causal mask as well.  Token tok of the block and key
+    // key0 + c meet at x = (tok_per_tile - 1 - tok) + c; the two parities make every pair (x, x + 1) an aligned 8 bytes.
+    auto stage_bias = [&](int key0) {
+        const int d0 = pos_first + tok_per_tile - 1 - key0;
+        int h = threadIdx.x / (2 * XS), y = threadIdx.x - h * 2 * XS;
+        const int dh = kBiasThreads / (2 * XS), dy = kBiasThreads - dh * 2 * XS;
+        for (; h < g; h += dh, y += dy) {
+            if (y >= 2 * XS) { y -= 2 * XS; ++h; if (h >= g) break; }
+            const int par = y >= XS ? 1 : 0;
+            const int d = d0 - (y - par * XS + par);
+            sB[h * 2 * XS + y] = d < 0 ? -INFINITY : __ldg(p.bias + static_cast<int64_t>(kvh * g + h) * p.L + min(d, p.L - 1)) * kLog2eBias;
+        }
+    };
 
     float o[W / 8][4];
 #pragma unroll
@@ -142,6 +169,9 @@ attn_bias_kernel(const BiasAttnParams p) {
     for (int it = 0; it < n_tiles; ++it) {
         if (it + 1 < n_tiles) load_tile(it + 1, (it + 1) & 1);
         cp_async_commit();
+        const int key0 = it * kBiasTileKeys;
+        const bool all_far = pos_first - (key0 + kBiasTileKeys - 1) >= p.L - 1;   // every key of the tile beyond the table, for every token
+        if (!all_far) stage_bias(key0);
         cp_async_wait<1>();                               // everything but the newest group: the query tile and tile `it`
         __syncthreads();
         if (it == 0) {
@@ -151,7 +181,6 @@ attn_bias_kernel(const BiasAttnParams p) {
                 ldm_x4(qf[ks], sQ + (warp * 16 + (lane & 15)) * LDQ + ks * 16 + (lane >> 4) * 8);
             }
         }
-        const int key0 = it * kBiasTileKeys;
         if (warp_has_rows && key0 <= warp_last_pos) {
             const __nv_bfloat16* tile = sK + (it & 1) * kBiasTileKeys * LD;
             float s[8][4];
@@ -168,24 +197,19 @@ attn_bias_kernel(const BiasAttnParams p) {
                     mma_16816(s[np * 2 + 1], qf[ks], b[2], b[3]);
                 }
             }
-            // scale, bias, mask, running maximum and sum
-            const bool all_far = warp_first_pos - (key0 + kBiasTileKeys - 1) >= p.L - 1;   // every key of the tile beyond the table
+            // scale, bias (which is the mask too), running maximum and sum
             float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
             for (int nt = 0; nt < 8; ++nt) {
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const int half = e >> 1;
-                    const int j = key0 + nt * 8 + ((lane & 3) << 1) + (e & 1);
-                    const int dist = row_hi[half] - j;
-                    float v = -INFINITY;
-                    if (dist >= 0) {
-                        const float b = (all_far || dist >= p.L - 1) ? bfar[half] : __ldg(brow[half] + dist) * kLog2eBias;
-                        v = fmaf(s[nt][e], p.scale_log2, b);
-                    }
-                    s[nt][e] = v;
-                    mx[half] = fmaxf(mx[half], v);
-                }
+                float2 b0, b1;
+                if (all_far) { b0.x = b0.y = bfar[0]; b1.x = b1.y = bfar[1]; }
+                else { b0 = tb[0][nt * 4]; b1 = tb[1][nt * 4]; }
+                s[nt][0] = fmaf(s[nt][0], p.scale_log2, b0.x);
+                s[nt][1] = fmaf(s[nt][1], p.scale_log2, b0.y);
+                s[nt][2] = fmaf(s[nt][2], p.scale_log2, b1.x);
+                s[nt][3] = fmaf(s[nt][3], p.scale_log2, b1.y);
+                mx[0] = fmaxf(mx[0], fmaxf(s[nt][0], s[nt][1]));
+                mx[1] = fmaxf(mx[1], fmaxf(s[nt][2], s[nt][3]));
             }
             float corr[2];
 #pragma unroll
@@ -260,8 +284,8 @@ attn_bias_kernel(const BiasAttnParams p) {
 // A block owns one (request, kv head): the g <= 16 query heads of the group are the rows of ONE 16-row slab, and each of
 // the block's warps takes every n-th key tile (32 entries) for itself: it fetches its tiles into two stages of its own
 // (cp.async by its own lanes, __syncwarp, no block-wide barrier in the loop), keeps its own running maximum, sum and
-// accumulator, and the warps' partial results are merged through shared memory at the end.  Eight warps, or four where
-// the entries are so wide that eight warps' stages would not fit.  When few (request, kv head) pairs would leave SMs
+// accumulator, and the warps' partial results are merged through shared memory at the end.  Eight warps, or as many
+// as have room for their stages where the entries are wide (six at 128 + 128 elements).  When few (request, kv head) pairs would leave SMs
 // idle, the tiles are shared out among `splits` blocks as well, which leave their parts in scratch for a merge kernel.
 template <int W>
 __global__ void __launch_bounds__(256)
@@ -292,13 +316,16 @@ attn_bias_decode_kernel(const BiasAttnParams p) {
     cp_async_commit();
 
     __nv_bfloat16* my = sK + warp * 2 * kBiasDecKeys * LD;
+    const int ld_r0 = lane / CE, ld_c0 = lane - ld_r0 * CE;
+    const int ld_dr = 32 / CE, ld_dc = 32 - ld_dr * CE;
     auto load_tile = [&](int it, int stage) {
         const int key0 = it * kBiasDecKeys;
         __nv_bfloat16* dst = my + stage * kBiasDecKeys * LD;
         int last_slot = -1, page = -1;
         const __nv_bfloat16* page_base = p.pages;
-        for (int i = lane; i < kBiasDecKeys * CE; i += 32) {
-            const int r = i / CE, c = i - r * CE;
+        int r = ld_r0, c = ld_c0;                         // chunk lane + 32 n is row (lane + 32 n) / CE: kept by increments
+        for (; r < kBiasDecKeys; r += ld_dr, c += ld_dc) {
+            if (c >= CE) { c -= CE; ++r; if (r >= kBiasDecKeys) break; }
             const int j = key0 + r;
             bool need = j <= pos;
             const __nv_bfloat16* src = p.pages;
@@ -501,7 +528,10 @@ __global__ void attn_bias_merge_kernel(const BiasAttnParams p) {
 template <int W>
 int launch_attn_bias_decode(const BiasAttnParams& p, cudaStream_t stream) {
     const int E = p.dk + p.dv;
-    const int nw = E > 192 ? 4 : 8;
+    // as many warps as their stages leave room for, eight at most
+    const size_t per_warp = static_cast<size_t>(2) * kBiasDecKeys * (E + 8) * sizeof(__nv_bfloat16) + 16 * 2 * sizeof(float);
+    const size_t room = 216 * 1024 - static_cast<size_t>(16) * (p.dk + 8) * sizeof(__nv_bfloat16);
+    const int nw = room / per_warp >= 8 ? 8 : static_cast<int>(room / per_warp);
     const size_t smem = (static_cast<size_t>(16) * (p.dk + 8) + static_cast<size_t>(nw) * 2 * kBiasDecKeys * (E + 8)) * sizeof(__nv_bfloat16)
                         + nw * 16 * 2 * sizeof(float);
     static bool raised = false;
@@ -518,10 +548,12 @@ int launch_attn_bias_decode(const BiasAttnParams& p, cudaStream_t stream) {
 template <int W>
 int launch_attn_bias(const BiasAttnParams& p, int num_tiles, cudaStream_t stream) {
     const int E = p.dk + p.dv;
-    const size_t smem = (static_cast<size_t>(kBiasTileRows) * (p.dk + 8) + static_cast<size_t>(2) * kBiasTileKeys * (E + 8)) * sizeof(__nv_bfloat16);
+    const int g = p.H / p.G;
+    const size_t smem = (static_cast<size_t>(kBiasTileRows) * (p.dk + 8) + static_cast<size_t>(2) * kBiasTileKeys * (E + 8)) * sizeof(__nv_bfloat16)
+                        + static_cast<size_t>(g) * 2 * bias_row_floats(kBiasTileRows / g) * sizeof(float);
     static bool raised = false;
     if (!raised) {
-        if (cudaFuncSetAttribute(attn_bias_kernel<W>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024) != cudaSuccess)
+        if (cudaFuncSetAttribute(attn_bias_kernel<W>, cudaFuncAttributeMaxDynamicSharedMemorySize, 136 * 1024) != cudaSuccess)
             return launch_status();
         raised = true;
     }

@@ -118,6 +118,29 @@ __global__ void glu_clamped_kernel(T* __restrict__ out, const T* __restrict__ gu
     }
 }
 
+// 16 bytes of gate and of up per thread: I is a multiple of the chunk and all rows start on 16 bytes
+template <typename T>
+__global__ void glu_clamped_vec_kernel(T* __restrict__ out, const T* __restrict__ gu, int64_t n_chunks, int I, float limit, float alpha) {
+    pdl_trigger();
+    pdl_wait();
+    constexpr int N = 16 / sizeof(T);
+    const int64_t k = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (k >= n_chunks) return;
+    const int per_row = I / N;
+    const int64_t t = k / per_row;
+    const int c = static_cast<int>(k - t * per_row) * N;
+    alignas(16) T g[N], u[N], o[N];
+    *reinterpret_cast<uint4*>(g) = *reinterpret_cast<const uint4*>(gu + t * 2 * I + c);
+    *reinterpret_cast<uint4*>(u) = *reinterpret_cast<const uint4*>(gu + t * 2 * I + I + c);
+#pragma unroll
+    for (int i = 0; i < N; ++i) {
+        const float gi = fminf(to_float(g[i]), limit);
+        const float ui = fminf(fmaxf(to_float(u[i]), -limit), limit);
+        o[i] = from_float<T>(gi * sigmoid_f(alpha * gi) * (ui + 1.f));
+    }
+    *reinterpret_cast<uint4*>(out + t * I + c) = *reinterpret_cast<const uint4*>(o);
+}
+
 template <typename T>
 __global__ void add_gated_rows_kernel(T* __restrict__ y, const T* __restrict__ s, const float* __restrict__ z, int z_stride, int64_t n,
                                       int D) {
@@ -214,7 +237,14 @@ extern "C" int cvb_glu_clamped(void* out, const void* gate_up, int T, int I, flo
     if (T < 0 || I <= 0) return CVB_E_SIZE;
     const int64_t n = static_cast<int64_t>(T) * I, want = (n + 255) / 256;
     const unsigned blocks = static_cast<unsigned>(want < 148 * 16 ? want : 148 * 16);
-#define CALL(TY) launch_kernel(glu_clamped_kernel<TY>, dim3(blocks), dim3(256), 0, stream, (TY*)out, (const TY*)gate_up, n, I, limit, alpha)
+    const bool aligned = ((reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(gate_up)) & 15) == 0;
+#define CALL(TY)                                                                                                                          \
+    if (aligned && I % (16 / (int)sizeof(TY)) == 0) {                                                                                     \
+        const int64_t nc = n / (16 / (int)sizeof(TY));                                                                                    \
+        launch_kernel(glu_clamped_vec_kernel<TY>, dim3(static_cast<unsigned>((nc + 255) / 256)), dim3(256), 0, stream, (TY*)out,          \
+                      (const TY*)gate_up, nc, I, limit, alpha);                                                                           \
+    } else                                                                                                                                \
+        launch_kernel(glu_clamped_kernel<TY>, dim3(blocks), dim3(256), 0, stream, (TY*)out, (const TY*)gate_up, n, I, limit, alpha)
     CVB_DISPATCH_DTYPE(dtype, CALL);
 #undef CALL
     return launch_status();

@@ -20,6 +20,16 @@ head in the two recurrent mixers.  Its kernels are timed beside the Qwen3 kernel
 beside grouped-query attention (prompt and decode), the two scans beside prompt attention (both are the mixer's core over
 2,048 tokens) and, for decoded tokens, as bytes of state over the copy bandwidth, the norm behind a sublayer beside the
 fused add-and-norm, bias and squared relu beside SwiGLU.
+
+    python bench.py --design lorulix
+
+The Lorulix model of a size has the same width, heads and head size; its layers repeat the pattern [attention with a dense
+clamped feed-forward, head delta with experts, attention reading the first one's cache with experts, head delta with a dense
+feed-forward]: a distance table of 32 rows up to distance 1,024, a query temperature, input convolutions of 4 taps, 8
+squared-relu experts of half the inner size, 2 per token, with a shared expert.  Whole models stand beside Givirax (the closest
+existing model: a float32 stream, attention over cache entries, routed experts) and Qwen3; its kernels beside the like kernels of
+Givirax (attention, experts), Dugulorn (the delta rule, the norm behind a sublayer) and Qwen3 (the projection's epilogue, the
+activation).
 """
 from __future__ import annotations
 
@@ -39,6 +49,7 @@ SIZES = {
     "large": dict(width=4096, heads=32, kv_heads=8, dim=128, ff=12288, layers=4, vocab=32000),
 }
 WINDOW, KEEP, EXPERTS, TOP = 1024, 4, 8, 2
+BIAS_ROWS, BIAS_FAR = 32, 1024
 
 
 def givirax_config(s, max_positions):
@@ -69,6 +80,31 @@ def dugulorn_config(s, max_positions):
                     "mlp": None}]
     return {"architecture": "Dugulorn", "vocab": s["vocab"], "width": D, "max_positions": max_positions, "norm": {"eps": 1e-5},
             "layers": layers[:s["layers"]]}
+
+
+def lorulix_config(s, max_positions):
+    H, KV, hd, I = s["heads"], s["kv_heads"], s["dim"], s["ff"]
+
+    def attention(src=None):
+        m = {"dim": hd, "heads": H, "kv_heads": KV, "vdim": hd, "scale": 1.0 / math.sqrt(hd), "bias_max": BIAS_FAR, "bias_rows": BIAS_ROWS,
+             "q_temp": {"coef": 0.25, "every": 128}}
+        if src is not None:
+            m["kv_from"] = src
+        return m
+    delta = {"dim": hd, "heads": H, "kv_heads": KV, "vdim": hd, "conv": 4}
+    dense = {"kind": "dense", "ff": I, "limit": 7.0}
+    moe = {"kind": "moe", "expert": {"ff": I // 2}, "router": {"experts": EXPERTS, "top": TOP, "scale": 1.0}, "shared": {"ff": I // 2}}
+    layers = []
+    for i in range(s["layers"]):
+        k = i % 4
+        if k == 0:
+            layers.append({"type": "attention", "mixer": attention(), "mlp": dense})
+        elif k == 2:
+            layers.append({"type": "attention", "mixer": attention(i - 2), "mlp": moe})
+        else:
+            layers.append({"type": "delta", "mixer": delta, "mlp": moe if k == 1 else dense})
+    return {"architecture": "Lorulix", "vocab": s["vocab"], "width": s["width"], "max_positions": max_positions,
+            "norm": {"eps": 1e-5}, "canon": {"taps": 4}, "layers": layers}
 
 
 def qwen3_config(s, max_positions):
@@ -432,9 +468,190 @@ def dugulorn_kernel_pairs(s, pk):
     return out
 
 
+def lorulix_kernel_pairs(s, pk):
+    """The kernels that the Lorulix parts brought, each beside the like kernel of an existing model at the same sizes (`like`
+    names it)."""
+    from .csrc import ops
+    d = torch.device("cuda:0")
+    g = torch.Generator(device="cuda").manual_seed(0)
+    bf, f32, i32 = torch.bfloat16, torch.float32, torch.int32
+    D, H, KV, hd, I = s["width"], s["heads"], s["kv_heads"], s["dim"], s["ff"]
+    F = I // 2
+    page, out = 32, {}
+    hbm, flop = pk["hbm_gbs"] * 1e9, pk["bf16_tflops"] * 1e12
+
+    def rnd(*shape, scale=1.0, dtype=bf):
+        return (torch.randn(*shape, generator=g, device=d, dtype=f32) * scale).to(dtype)
+
+    def pair(name, new_us, new_work, like_us, like_work, unit, like, note=None):
+        peak = hbm if unit == "bytes" else flop
+        fn, fl = new_work / (new_us * 1e-6) / peak, like_work / (like_us * 1e-6) / peak
+        out[name] = {"new_us": round(new_us, 2), "new_frac": round(fn, 4), "like_us": round(like_us, 2), "like_frac": round(fl, 4),
+                     "gap": round(fl / fn, 2), "roofline": "copy bandwidth" if unit == "bytes" else "bf16 peak", "like": like}
+        if note:
+            out[name]["note"] = note
+
+    def alone(name, new_us, work, note="no like kernel in an existing model"):
+        out[name] = {"new_us": round(new_us, 2), "new_frac": round(work / (new_us * 1e-6) / hbm, 4), "roofline": "copy bandwidth", "note": note}
+
+    # -- attention of a prompt of 2,048 tokens ---------------------------------------------------------------------------
+    T = 2048
+    n_pages = T // page
+    flops = 4.0 * H * hd * T * (T + 1) / 2
+    tables = torch.arange(n_pages, dtype=i32, device=d).view(1, n_pages)
+    cu = torch.tensor([0, T], dtype=i32, device=d)
+    pos = torch.arange(T, dtype=i32, device=d)
+    seq_of = torch.zeros(T, dtype=i32, device=d)
+    scale = 1 / math.sqrt(hd)
+    entries = rnd(n_pages + 1, KV, page, 2 * hd)
+    q = rnd(T, H * hd)
+    att = torch.empty(T, H * hd, dtype=bf, device=d)
+    bias = rnd(H, BIAS_FAR + 1, dtype=f32)
+    tiles = ops.attn_keys_tiles([T], H, KV)
+    new = _us(lambda i: ops.attn_bias_bf16(att, q, entries, tables, cu, pos, 1, tiles, H, KV, hd, hd, page, scale, bias))
+    keys_pages = rnd(n_pages + 1, KV, page, hd)
+    qk = rnd(T, (H + KV) * hd)
+    like = _us(lambda i: ops.attn_keys_bf16(att, qk, keys_pages, tables, cu, pos, 1, tiles, H, KV, hd, page, scale))
+    pair("attention_prefill_2048", new, flops, like, flops, "flops", "Givirax attn_keys_kernel, no window")
+    kv_pages = rnd(n_pages + 1, 2, KV, page, hd)
+    tiles_tc = ops.prefill_tiles_tcgen05([T], H, KV)
+    like_tc = _us(lambda i: ops.attn_prefill_tcgen05(att, q, kv_pages, tables, cu, pos, 1, tiles_tc, H, KV, hd, page, scale))
+    out["attention_prefill_2048"]["qwen3_tcgen05_us"] = round(like_tc, 2)
+    out["attention_prefill_2048"]["qwen3_tcgen05_frac"] = round(flops / (like_tc * 1e-6) / flop, 4)
+
+    # -- attention of decoded tokens: batch 8 at 4,096 tokens ---------------------------------------------------------------
+    B, ctx = 8, 4096
+    pps = ctx // page
+    copies = 4
+    tabs = [torch.randperm(B * pps, generator=g, device=d).to(i32).view(B, pps).contiguous() for _ in range(copies)]
+    ent_big = [rnd(B * pps + 1, KV, page, 2 * hd) for _ in range(copies)]
+    keys_big = [rnd(B * pps + 1, KV, page, hd) for _ in range(copies)]
+    kv_big = [rnd(B * pps + 1, 2, KV, page, hd) for _ in range(copies)]
+    cu_b = torch.arange(0, B + 1, dtype=i32, device=d)
+    pos_b = torch.full((B,), ctx - 1, dtype=i32, device=d)
+    q_b, qk_b = rnd(B, H * hd), rnd(B, (H + KV) * hd)
+    att_b = torch.empty(B, H * hd, dtype=bf, device=d)
+    z = ops.attn_keys_decode_splits(B, KV, ctx)
+    parts = torch.empty(max(1, ops.attn_keys_scratch_floats(B, KV, hd, z)), dtype=f32, device=d)
+    new = _us(lambda i: ops.attn_bias_bf16(att_b, q_b, ent_big[i % copies], tabs[i % copies], cu_b, pos_b, B, B, H, KV, hd, hd, page, scale,
+                                           bias, all_single=True, splits=z, scratch=parts))
+    like = _us(lambda i: ops.attn_keys_bf16(att_b, qk_b, keys_big[i % copies], tabs[i % copies], cu_b, pos_b, B, B, H, KV, hd, page, scale,
+                                            all_single=True, splits=z, scratch=parts))
+    pair("attention_decode_b8_ctx_4096", new, B * ctx * KV * hd * 4.0, like, B * ctx * KV * hd * 2.0, "bytes", "Givirax attn_keys_decode_kernel, no window")
+    splits = 4
+    scratch = torch.empty(max(1, ops.attn_decode_scratch_floats(B, KV, hd, splits)), dtype=f32, device=d)
+    like_q = _us(lambda i: ops.attn_decode_bf16(att_b, q_b, kv_big[i % copies], tabs[i % copies], cu_b, pos_b, B, H, KV, hd, page, scale,
+                                                splits, scratch))
+    out["attention_decode_b8_ctx_4096"]["qwen3_us"] = round(like_q, 2)
+    out["attention_decode_b8_ctx_4096"]["qwen3_frac"] = round(B * ctx * KV * hd * 4.0 / (like_q * 1e-6) / hbm, 4)
+    del ent_big, keys_big, kv_big
+
+    # -- the projection's epilogue, 2,048 tokens: norms over the whole projections, temperature, cache write ------------------
+    packed = rnd(T, (H + 2 * KV) * hd)
+    q_out = torch.empty(T, H * hd, dtype=bf, device=d)
+    wq, wk = torch.ones(H * hd, device=d), torch.ones(KV * hd, device=d)
+    slots_t = torch.arange(T, dtype=i32, device=d)
+    new = _us(lambda i: ops.wide_qk_prep(q_out, packed, wq, pos, 1e-5, 0.25, 128, KV, hd, hd, pages=entries, k_weight=wk, slots=slots_t, page_size=page))
+    cos, sin = torch.rand(T, hd // 2, generator=g, device=d), torch.rand(T, hd // 2, generator=g, device=d)
+    w1 = torch.ones(hd, device=d)
+    like = _us(lambda i: ops.qk_norm_rope_kv(q_out, packed, w1, w1, cos, sin, pos, slots_t, kv_pages, H, KV, hd, page, 1e-6))
+    moved = T * (H + 2 * KV) * hd * 4.0
+    pair("projection_epilogue_2048_tokens", new, moved, like, moved, "bytes", "Qwen3 qk_norm_rope_kv")
+
+    # -- the delta rule with one decay per head: 2,048 tokens of one request, and 8 decoded tokens ----------------------------
+    C = 2 * KV * hd + H * hd
+    slots1 = torch.zeros(1, dtype=i32, device=d)
+    state = torch.zeros(2, H * hd * hd + 3 * C, dtype=f32, device=d)
+    o32 = torch.empty(T, H * hd, dtype=f32, device=d)
+    qn, kn, vv = rnd(T, KV * hd, dtype=f32, scale=0.05), rnd(T, KV * hd, dtype=f32, scale=0.05), rnd(T, H * hd, dtype=f32)
+    g1, gd, bb = torch.rand(T, H, generator=g, device=d), torch.rand(T, H * hd, generator=g, device=d), torch.rand(T, H, generator=g, device=d)
+    new = _us(lambda i: ops.delta_scan(o32, qn, kn, vv, g1, bb, state, cu, slots1, 1, H, KV, hd, hd, decay_dim=1))
+    like = _us(lambda i: ops.delta_scan(o32, qn, kn, vv, gd, bb, state, cu, slots1, 1, H, KV, hd, hd))
+    work = 6.0 * H * hd * hd * T
+    pair("delta_prefill_2048", new, work, like, work, "flops", "Dugulorn delta_scan with a decay per key channel",
+         note="a token-by-token scan on the float units; neither comes near the tensor peak")
+    raw, conv_w = rnd(T, C), rnd(C, 4, dtype=f32)
+    a1, ad, b32 = rnd(T, H, dtype=f32), rnd(T, H * hd, dtype=f32), rnd(T, H, dtype=f32)
+    dt1, dtd, alog = rnd(H, dtype=f32), rnd(H * hd, dtype=f32), rnd(H, dtype=f32)
+    new = _us(lambda i: ops.delta_prep(qn, kn, vv, g1, bb, raw, 0, conv_w, a1, dt1, alog, b32, state, H * hd * hd, seq_of, cu, slots1, H, KV, hd, hd, decay_dim=1))
+    like = _us(lambda i: ops.delta_prep(qn, kn, vv, gd, bb, raw, 0, conv_w, ad, dtd, alog, b32, state, H * hd * hd, seq_of, cu, slots1, H, KV, hd, hd))
+    pair("delta_prep_2048", new, T * (C * 2 + (2 * KV * hd + H * hd) * 4.0 + H * 16.0), like, T * (C * 2 + H * hd * 4 + (2 * KV * hd + 2 * H * hd) * 4.0),
+         "bytes", "Dugulorn delta_prep with a decay per key channel")
+    Bs = 8
+    n_copy = max(2, int(300e6 // (Bs * H * hd * hd * 4)) + 1)
+    states = [torch.zeros(Bs + 1, H * hd * hd, dtype=f32, device=d) for _ in range(n_copy)]
+    cu8, slots8 = torch.arange(0, Bs + 1, dtype=i32, device=d), torch.arange(0, Bs, dtype=i32, device=d)
+    new = _us(lambda i: ops.delta_scan(o32[:Bs], qn[:Bs], kn[:Bs], vv[:Bs], g1[:Bs], bb[:Bs], states[i % n_copy], cu8, slots8, Bs, H, KV, hd, hd, decay_dim=1))
+    like = _us(lambda i: ops.delta_scan(o32[:Bs], qn[:Bs], kn[:Bs], vv[:Bs], gd[:Bs], bb[:Bs], states[i % n_copy], cu8, slots8, Bs, H, KV, hd, hd))
+    work = Bs * H * hd * hd * 8.0
+    pair("delta_decode_b8", new, work, like, work, "bytes", "Dugulorn delta_scan with a decay per key channel")
+    del states
+    gate16, y16, wn = rnd(T, H * hd), torch.empty(T, H * hd, dtype=bf, device=d), torch.ones(hd, device=d)
+    new = _us(lambda i: ops.gated_norm(y16, o32, gate16, wn, H, 1e-5, gate_act="silu"))
+    like = _us(lambda i: ops.gated_norm(y16, o32, gate16, wn, H, 1e-5))
+    pair("gated_norm_2048_tokens", new, T * H * hd * 8.0, like, T * H * hd * 8.0, "bytes", "Dugulorn gated_norm with the logistic gate")
+
+    # -- the block: input convolution, and the kernel that closes a sublayer ---------------------------------------------------
+    a16, x16, yy, zz, nxt = rnd(T, D), torch.empty(T, D, dtype=bf, device=d), rnd(T, D), rnd(T, D), torch.empty(T, D, dtype=bf, device=d)
+    h32 = torch.randn(T, D, generator=g, device=d)
+    taps = rnd(D, 4, dtype=f32)
+    hist = torch.zeros(2, 3 * D, dtype=f32, device=d)
+    new = _us(lambda i: ops.input_conv(x16, a16, taps, hist, 0, seq_of, cu, slots1))
+    alone("input_convolution_2048_tokens", new, T * D * 4.0)
+    w, bz = torch.ones(D, device=d), torch.zeros(D, device=d)
+    new = _us(lambda i: ops.gated_norm_add(h32, yy, w, 1e-5, gate=zz, gate_bias=bz, next_weight=w, next_eps=1e-5, next_out=nxt,
+                                           history=(a16, 4, hist, 0, seq_of, cu, slots1)))
+    copy = torch.empty(T, D, dtype=bf, device=d)
+    like = _us(lambda i: ops.norm_add(h32, yy, w, 1e-5, bias=bz, copy=copy))
+    pair("sublayer_close_2048_tokens", new, T * D * (4 + 4 + 2 + 2 + 2.0), like, T * D * (4 + 4 + 2 + 2.0), "bytes", "Dugulorn norm_add",
+         note="also the gate, the next sublayer's norm and the convolution's history")
+    h16, normed = rnd(T, D), torch.empty(T, D, dtype=bf, device=d)
+    like_q = _us(lambda i: ops.add_rmsnorm(normed, h16, yy, w, 1e-6))
+    out["sublayer_close_2048_tokens"]["qwen3_add_rmsnorm_us"] = round(like_q, 2)
+    out["sublayer_close_2048_tokens"]["qwen3_add_rmsnorm_frac"] = round(T * D * 8.0 / (like_q * 1e-6) / hbm, 4)
+
+    # -- feed-forwards ---------------------------------------------------------------------------------------------------------
+    gu_t, act = rnd(T, 2 * I), torch.empty(T, I, dtype=bf, device=d)
+    new = _us(lambda i: ops.glu_clamped(act, gu_t, 7.0, 1.702))
+    like = _us(lambda i: ops.swiglu(act, gu_t))
+    pair("activation_2048_tokens", new, T * I * 6.0, like, T * I * 6.0, "bytes", "Qwen3 swiglu")
+    x = rnd(T, D)
+    w_router = torch.randn(EXPERTS + 1, D, generator=g, device=d)
+    ids, wts = torch.empty(T, TOP, dtype=i32, device=d), torch.empty(T, TOP, dtype=f32, device=d)
+    sg = torch.empty(T, 1, dtype=f32, device=d)
+    new = _us(lambda i: ops.route_topk(ids, wts, x, w_router, None, over_all=True, scale=1.0, extra_out=sg))
+    w_r8, b_r8 = w_router[:EXPERTS].contiguous(), torch.zeros(EXPERTS, device=d)
+    ids2, wts2 = torch.empty(T, TOP, dtype=i32, device=d), torch.empty(T, TOP, dtype=f32, device=d)
+    like = _us(lambda i: ops.route_topk(ids2, wts2, x, w_r8, b_r8))
+    pair("router_2048_tokens", new, T * D * 2.0, like, T * D * 2.0, "bytes", "Givirax route_topk")
+    from .parts.base import Workspace
+    ws = Workspace(d, T)
+    w_up, w_dn = rnd(EXPERTS, F, D, scale=0.02), rnd(EXPERTS, D, F, scale=0.02)
+    w_gu = rnd(EXPERTS, 2 * F, D, scale=0.02)
+    y = torch.empty(T, D, dtype=bf, device=d)
+    new = _us(lambda i: ops.routed_experts(y, x, ids, wts, w_up, w_dn, workspace=ws, gated=False))
+    like = _us(lambda i: ops.routed_experts(y, x, ids2, wts2, w_gu, w_dn, workspace=ws))
+    pair("experts_2048_tokens", new, 2.0 * T * TOP * 2 * D * F, like, 2.0 * T * TOP * 3 * D * F, "flops", "Givirax gated experts")
+    ws8 = Workspace(d, 8)
+    copies = max(2, int(300e6 // (w_gu.numel() * 2 + w_dn.numel() * 2)) + 1)
+    ups = [w_up] + [rnd(EXPERTS, F, D, scale=0.02) for _ in range(copies - 1)]
+    gus = [w_gu] + [rnd(EXPERTS, 2 * F, D, scale=0.02) for _ in range(copies - 1)]
+    dns = [w_dn] + [rnd(EXPERTS, D, F, scale=0.02) for _ in range(copies - 1)]
+    x8, y8 = x[:8].contiguous(), torch.empty(8, D, dtype=bf, device=d)
+    ids8, wts8, ids28, wts28 = ids[:8].contiguous(), wts[:8].contiguous(), ids2[:8].contiguous(), wts2[:8].contiguous()
+    new = _us(lambda i: ops.routed_experts(y8, x8, ids8, wts8, ups[i % copies], dns[i % copies], workspace=ws8, gated=False))
+    like = _us(lambda i: ops.routed_experts(y8, x8, ids28, wts28, gus[i % copies], dns[i % copies], workspace=ws8))
+    used, used2 = len(set(ids8.flatten().tolist())), len(set(ids28.flatten().tolist()))
+    pair("experts_8_decoded_tokens", new, used * 2.0 * D * F * 2, like, used2 * 3.0 * D * F * 2, "bytes", "Givirax gated experts")
+    s16, zt = rnd(T, D), torch.rand(T, generator=g, device=d)
+    new = _us(lambda i: ops.add_gated_rows(y, s16, zt))
+    alone("shared_expert_sum_2048_tokens", new, T * D * 6.0)
+    return out
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="design_bench", description=__doc__.split("\n\n")[0])
-    ap.add_argument("--design", default="givirax", choices=["givirax", "dugulorn"])
+    ap.add_argument("--design", default="givirax", choices=["givirax", "dugulorn", "lorulix"])
     ap.add_argument("--sizes", default="small,large")
     ap.add_argument("--steps", type=int, default=48)
     ap.add_argument("--no-kernels", action="store_true", help="whole models only")
@@ -449,17 +666,21 @@ def main(argv=None) -> int:
     result = {"design": a.design, "closest": "Qwen3ForCausalLM", "dtype": "bf16", "data": "synthetic, random weights", "peaks": pk, "sizes": {}}
     if a.design == "givirax":
         result.update(window=WINDOW, keep_first=KEEP, experts=EXPERTS, top=TOP)
+    if a.design == "lorulix":
+        result.update(closest="Givirax", bias_rows=BIAS_ROWS, bias_far=BIAS_FAR, experts=EXPERTS, top=TOP)
     for name in a.sizes.split(","):
         s = SIZES[name]
         entry = {"shape": s}
         if not a.no_models:
             t0 = time.time()
-            design_config = givirax_config if a.design == "givirax" else dugulorn_config
+            design_config = {"givirax": givirax_config, "dugulorn": dugulorn_config, "lorulix": lorulix_config}[a.design]
             entry[a.design] = model_points(design_config(s, 4160), 2048, 8, 4096, a.steps)
+            if a.design == "lorulix":
+                entry["givirax"] = model_points(givirax_config(s, 4160), 2048, 8, 4096, a.steps)
             entry["qwen3"] = model_points(qwen3_config(s, 4160), 2048, 8, 4096, a.steps)
             entry["seconds"] = round(time.time() - t0, 1)
         if not a.no_kernels:
-            entry["kernels"] = kernel_pairs(s, pk) if a.design == "givirax" else dugulorn_kernel_pairs(s, pk)
+            entry["kernels"] = {"givirax": kernel_pairs, "dugulorn": dugulorn_kernel_pairs, "lorulix": lorulix_kernel_pairs}[a.design](s, pk)
         result["sizes"][name] = entry
     print(json.dumps(result))
     return 0

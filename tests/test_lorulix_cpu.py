@@ -84,7 +84,7 @@ def test_run_list_caches_states_and_tensor_names():
 
 
 def test_distance_buckets():
-    for rows, far in ((32, 240), (8, 20), (6, 9), (4, 3), (12, 50), (16, 300), (64, 4096)):
+    for rows, far in ((32, 384), (8, 20), (6, 9), (4, 3), (12, 50), (16, 300), (64, 4096)):
         table = distance_buckets(rows, far)
         assert table == [plain.distance_bucket(n, rows, far) for n in range(far + 1)]
         half = rows // 2
@@ -92,9 +92,9 @@ def test_distance_buckets():
         assert all(b >= a for a, b in zip(table, table[1:]))
         assert all(plain.distance_bucket(n, rows, far) == rows - 1 for n in (far, far + 1, 10 * far))
     # a bucket's first distance by the closed form: the smallest n with half * (far / half)^((b - half) / (rows - half)) <= n
-    table = distance_buckets(32, 240)
+    table = distance_buckets(32, 384)
     for b in range(17, 32):
-        edge = 16 * (240 / 16) ** ((b - 16) / 16)
+        edge = 16 * (384 / 16) ** ((b - 16) / 16)
         first = table.index(b) if b in table else None
         assert first is None or first == math.ceil(edge - 1e-9)
     with pytest.raises(ValueError):

@@ -307,7 +307,7 @@ def test_head_norm_with_a_silu_gate(dtype, H, dv):
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("T,D,E,top,I,shared,scale", [(1, 48, 5, 2, 24, 16, 2.0), (2, 80, 3, 1, 16, 0, 1.0), (37, 96, 4, 4, 32, 32, 1.5),
-                                                      (70, 50, 6, 3, 12, 12, 2.5), (300, 256, 12, 3, 96, 96, 2.0)])
+                                                      (70, 50, 6, 3, 12, 12, 2.5), (300, 192, 10, 3, 80, 48, 2.0)])
 def test_router_over_all_experts_and_squared_relu_experts_with_a_gated_shared_one(dtype, T, D, E, top, I, shared, scale):
     """Through the part itself (what the model calls), with the simple kernels and with the ones a step of that size takes."""
     from cppvllm_b200.parts.base import Runtime, Workspace
