@@ -55,14 +55,16 @@ __device__ __forceinline__ void bias_page_of(const BiasAttnParams& p, int j, int
     else { slot = j / p.page_size; off = j - slot * p.page_size; }
 }
 
-template <int W>
+// EXACT: dk = dv = W, known to the compiler (no run-time bounds inside the unrolled loops, constant strides)
+template <int W, bool EXACT>
 __global__ void __launch_bounds__(kBiasThreads, W <= 64 ? 3 : 2)
 attn_bias_kernel(const BiasAttnParams p) {
     pdl_trigger();
     pdl_wait();
-    const int E = p.dk + p.dv;
-    const int LDQ = p.dk + 8, LD = E + 8;                 // padded rows, in elements
-    const int CQ = p.dk >> 3, CE = E >> 3;                // 16-byte chunks per row
+    const int dk = EXACT ? W : p.dk, dv = EXACT ? W : p.dv;
+    const int E = dk + dv;
+    const int LDQ = dk + 8, LD = E + 8;                   // padded rows, in elements
+    const int CQ = dk >> 3, CE = E >> 3;                  // 16-byte chunks per row
     extern __shared__ __align__(16) unsigned char smem_raw[];
     __nv_bfloat16* sQ = reinterpret_cast<__nv_bfloat16*>(smem_raw);
     __nv_bfloat16* sK = sQ + kBiasTileRows * LDQ;         // two stages of kBiasTileKeys * LD
@@ -95,7 +97,7 @@ attn_bias_kernel(const BiasAttnParams p) {
         const int r = i / CQ, c = i - r * CQ;
         const int tok = r / g;
         const bool valid = tok < n_tok;
-        const __nv_bfloat16* src = valid ? p.q + static_cast<int64_t>(cu0 + q0 + tok) * p.q_stride + (kvh * g + r % g) * p.dk + c * 8 : p.q;
+        const __nv_bfloat16* src = valid ? p.q + static_cast<int64_t>(cu0 + q0 + tok) * p.q_stride + (kvh * g + r % g) * dk + c * 8 : p.q;
         cp_async16(sQ + r * LDQ + c * 8, src, valid);
     }
 
@@ -177,7 +179,7 @@ attn_bias_kernel(const BiasAttnParams p) {
         if (it == 0) {
 #pragma unroll
             for (int ks = 0; ks < W / 16; ++ks) {
-                if (ks * 16 >= p.dk) break;
+                if (!EXACT && ks * 16 >= dk) break;
                 ldm_x4(qf[ks], sQ + (warp * 16 + (lane & 15)) * LDQ + ks * 16 + (lane >> 4) * 8);
             }
         }
@@ -188,7 +190,7 @@ attn_bias_kernel(const BiasAttnParams p) {
             for (int nt = 0; nt < 8; ++nt) { s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f; }
 #pragma unroll
             for (int ks = 0; ks < W / 16; ++ks) {
-                if (ks * 16 >= p.dk) break;
+                if (!EXACT && ks * 16 >= dk) break;
 #pragma unroll
                 for (int np = 0; np < 4; ++np) {
                     uint32_t b[4];
@@ -247,9 +249,9 @@ attn_bias_kernel(const BiasAttnParams p) {
                 a[3] = pack2(s[kk * 2 + 1][2], s[kk * 2 + 1][3]);
 #pragma unroll
                 for (int dp = 0; dp < W / 16; ++dp) {
-                    if (dp * 16 >= p.dv) break;
+                    if (!EXACT && dp * 16 >= dv) break;
                     uint32_t b[4];
-                    ldm_x4_trans(b, tile + (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LD + p.dk + dp * 16 + ((lane >> 4) & 1) * 8);
+                    ldm_x4_trans(b, tile + (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LD + dk + dp * 16 + ((lane >> 4) & 1) * 8);
                     mma_16816(o[dp * 2], a, b[0], b[1]);
                     mma_16816(o[dp * 2 + 1], a, b[2], b[3]);
                 }
@@ -269,11 +271,11 @@ attn_bias_kernel(const BiasAttnParams p) {
         const int tok = r / g;
         if (tok >= n_tok) continue;
         const float inv = l[half] > 0.f ? 1.f / l[half] : 0.f;
-        __nv_bfloat16* dst = p.out + (static_cast<int64_t>(cu0 + q0 + tok) * p.H + kvh * g + r % g) * p.dv;
+        __nv_bfloat16* dst = p.out + (static_cast<int64_t>(cu0 + q0 + tok) * p.H + kvh * g + r % g) * dv;
 #pragma unroll
         for (int dt = 0; dt < W / 8; ++dt) {
             const int d = dt * 8 + ((lane & 3) << 1);
-            if (d >= p.dv) break;
+            if (!EXACT && d >= dv) break;
             *reinterpret_cast<__nv_bfloat162*>(dst + d) = __floats2bfloat162_rn(o[dt][half * 2] * inv, o[dt][half * 2 + 1] * inv);
         }
     }
@@ -287,14 +289,15 @@ attn_bias_kernel(const BiasAttnParams p) {
 // accumulator, and the warps' partial results are merged through shared memory at the end.  Eight warps, or as many
 // as have room for their stages where the entries are wide (six at 128 + 128 elements).  When few (request, kv head) pairs would leave SMs
 // idle, the tiles are shared out among `splits` blocks as well, which leave their parts in scratch for a merge kernel.
-template <int W>
+template <int W, bool EXACT>
 __global__ void __launch_bounds__(256)
 attn_bias_decode_kernel(const BiasAttnParams p) {
     pdl_trigger();
     pdl_wait();
-    const int E = p.dk + p.dv;
-    const int LDQ = p.dk + 8, LD = E + 8;
-    const int CQ = p.dk >> 3, CE = E >> 3;
+    const int dk = EXACT ? W : p.dk, dv = EXACT ? W : p.dv;
+    const int E = dk + dv;
+    const int LDQ = dk + 8, LD = E + 8;
+    const int CQ = dk >> 3, CE = E >> 3;
     const int nw = blockDim.x >> 5;
     extern __shared__ __align__(16) unsigned char smem_raw[];
     __nv_bfloat16* sQ = reinterpret_cast<__nv_bfloat16*>(smem_raw);                    // [16][LDQ]
@@ -311,7 +314,7 @@ attn_bias_decode_kernel(const BiasAttnParams p) {
     for (int i = threadIdx.x; i < 16 * CQ; i += blockDim.x) {
         const int r = i / CQ, c = i - r * CQ;
         const bool valid = r < g;
-        cp_async16(sQ + r * LDQ + c * 8, valid ? p.q + static_cast<int64_t>(t) * p.q_stride + (kvh * g + r) * p.dk + c * 8 : p.q, valid);
+        cp_async16(sQ + r * LDQ + c * 8, valid ? p.q + static_cast<int64_t>(t) * p.q_stride + (kvh * g + r) * dk + c * 8 : p.q, valid);
     }
     cp_async_commit();
 
@@ -324,6 +327,22 @@ attn_bias_decode_kernel(const BiasAttnParams p) {
         int last_slot = -1, page = -1;
         const __nv_bfloat16* page_base = p.pages;
         int r = ld_r0, c = ld_c0;                         // chunk lane + 32 n is row (lane + 32 n) / CE: kept by increments
+        if (p.page_shift >= 5) {
+            // pages of 32 tokens and more (a power of two): the tile lies in ONE page, its rows side by side
+            const int slot = key0 >> p.page_shift;
+            page = slot < p.table_width ? table[slot] : -1;
+            const bool ok = page >= 0 && page < p.num_pages;
+            if (!ok) atomicExch(p.err, 4);
+            const __nv_bfloat16* base = ok ? p.pages + ((static_cast<int64_t>(page) * p.G + kvh) * p.page_size + (key0 & (p.page_size - 1))) * E
+                                           : p.pages;
+            const int live = ok ? pos - key0 : -1;        // rows 0..live hold keys the token sees
+            for (; r < kBiasDecKeys; r += ld_dr, c += ld_dc) {
+                if (c >= CE) { c -= CE; ++r; if (r >= kBiasDecKeys) break; }
+                const bool need = r <= live;
+                cp_async16(dst + r * LD + c * 8, need ? base + r * E + c * 8 : p.pages, need);
+            }
+            return;
+        }
         for (; r < kBiasDecKeys; r += ld_dr, c += ld_dc) {
             if (c >= CE) { c -= CE; ++r; if (r >= kBiasDecKeys) break; }
             const int j = key0 + r;
@@ -358,7 +377,7 @@ attn_bias_decode_kernel(const BiasAttnParams p) {
     uint32_t qf[W / 16][4];
 #pragma unroll
     for (int ks = 0; ks < W / 16; ++ks) {
-        if (ks * 16 >= p.dk) break;
+        if (!EXACT && ks * 16 >= dk) break;
         ldm_x4(qf[ks], sQ + (lane & 15) * LDQ + ks * 16 + (lane >> 4) * 8);
     }
     const float* brow[2];
@@ -388,7 +407,7 @@ attn_bias_decode_kernel(const BiasAttnParams p) {
         for (int nt = 0; nt < kBiasDecKeys / 8; ++nt) { s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f; }
 #pragma unroll
         for (int ks = 0; ks < W / 16; ++ks) {
-            if (ks * 16 >= p.dk) break;
+            if (!EXACT && ks * 16 >= dk) break;
 #pragma unroll
             for (int np = 0; np < kBiasDecKeys / 16; ++np) {
                 uint32_t b[4];
@@ -436,9 +455,11 @@ attn_bias_decode_kernel(const BiasAttnParams p) {
         }
 #pragma unroll
         for (int half = 0; half < 2; ++half) l[half] = l[half] * corr[half] + sum[half];
+        if (__any_sync(0xffffffffu, corr[0] != 1.f || corr[1] != 1.f)) {     // no row's maximum moved: nothing to rescale
 #pragma unroll
-        for (int dt = 0; dt < W / 8; ++dt) {
-            o[dt][0] *= corr[0]; o[dt][1] *= corr[0]; o[dt][2] *= corr[1]; o[dt][3] *= corr[1];
+            for (int dt = 0; dt < W / 8; ++dt) {
+                o[dt][0] *= corr[0]; o[dt][1] *= corr[0]; o[dt][2] *= corr[1]; o[dt][3] *= corr[1];
+            }
         }
 #pragma unroll
         for (int kk = 0; kk < kBiasDecKeys / 16; ++kk) {
@@ -449,9 +470,9 @@ attn_bias_decode_kernel(const BiasAttnParams p) {
             a[3] = pack2(s[kk * 2 + 1][2], s[kk * 2 + 1][3]);
 #pragma unroll
             for (int dp = 0; dp < W / 16; ++dp) {
-                if (dp * 16 >= p.dv) break;
+                if (!EXACT && dp * 16 >= dv) break;
                 uint32_t b[4];
-                ldm_x4_trans(b, tile + (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LD + p.dk + dp * 16 + ((lane >> 4) & 1) * 8);
+                ldm_x4_trans(b, tile + (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LD + dk + dp * 16 + ((lane >> 4) & 1) * 8);
                 mma_16816(o[dp * 2], a, b[0], b[1]);
                 mma_16816(o[dp * 2 + 1], a, b[2], b[3]);
             }
@@ -475,14 +496,14 @@ attn_bias_decode_kernel(const BiasAttnParams p) {
 #pragma unroll
         for (int dt = 0; dt < W / 8; ++dt) {
             const int d = dt * 8 + ((lane & 3) << 1);
-            if (d >= p.dv) break;
-            part[r * p.dv + d] = o[dt][half * 2];
-            part[r * p.dv + d + 1] = o[dt][half * 2 + 1];
+            if (!EXACT && d >= dv) break;
+            part[r * dv + d] = o[dt][half * 2];
+            part[r * dv + d + 1] = o[dt][half * 2 + 1];
         }
     }
     __syncthreads();
-    for (int i = threadIdx.x; i < g * p.dv; i += blockDim.x) {
-        const int r = i / p.dv, d = i - r * p.dv;
+    for (int i = threadIdx.x; i < g * dv; i += blockDim.x) {
+        const int r = i / dv, d = i - r * dv;
         float mm = -INFINITY;
         for (int w = 0; w < nw; ++w) mm = fmaxf(mm, red_ml[(w * 16 + r) * 2]);
         float ll = 0.f, acc = 0.f;
@@ -490,14 +511,14 @@ attn_bias_decode_kernel(const BiasAttnParams p) {
             const float mw = red_ml[(w * 16 + r) * 2];
             const float f = mw == -INFINITY ? 0.f : ex2(mw - mm);
             ll += red_ml[(w * 16 + r) * 2 + 1] * f;
-            acc += reinterpret_cast<const float*>(sK + w * 2 * kBiasDecKeys * LD)[r * p.dv + d] * f;
+            acc += reinterpret_cast<const float*>(sK + w * 2 * kBiasDecKeys * LD)[r * dv + d] * f;
         }
         if (p.splits == 1) {
-            p.out[(static_cast<int64_t>(t) * p.H + kvh * g + r) * p.dv + d] = __float2bfloat16_rn(ll > 0.f ? acc / ll : 0.f);
+            p.out[(static_cast<int64_t>(t) * p.H + kvh * g + r) * dv + d] = __float2bfloat16_rn(ll > 0.f ? acc / ll : 0.f);
         } else {
-            float* dst = p.parts + ((static_cast<int64_t>(seq) * p.G + kvh) * p.splits + blockIdx.z) * 16 * (p.dv + 2) + r * (p.dv + 2);
+            float* dst = p.parts + ((static_cast<int64_t>(seq) * p.G + kvh) * p.splits + blockIdx.z) * 16 * (dv + 2) + r * (dv + 2);
             dst[d] = acc;
-            if (d == 0) { dst[p.dv] = mm; dst[p.dv + 1] = ll; }
+            if (d == 0) { dst[dv] = mm; dst[dv + 1] = ll; }
         }
     }
 }
@@ -525,7 +546,7 @@ __global__ void attn_bias_merge_kernel(const BiasAttnParams p) {
     }
 }
 
-template <int W>
+template <int W, bool EXACT>
 int launch_attn_bias_decode(const BiasAttnParams& p, cudaStream_t stream) {
     const int E = p.dk + p.dv;
     // as many warps as their stages leave room for, eight at most
@@ -536,16 +557,16 @@ int launch_attn_bias_decode(const BiasAttnParams& p, cudaStream_t stream) {
                         + nw * 16 * 2 * sizeof(float);
     static bool raised = false;
     if (!raised) {
-        if (cudaFuncSetAttribute(attn_bias_decode_kernel<W>, cudaFuncAttributeMaxDynamicSharedMemorySize, 216 * 1024) != cudaSuccess)
+        if (cudaFuncSetAttribute(attn_bias_decode_kernel<W, EXACT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 216 * 1024) != cudaSuccess)
             return launch_status();
         raised = true;
     }
-    launch_kernel(attn_bias_decode_kernel<W>, dim3(p.S, p.G, p.splits), dim3(nw * 32), smem, stream, p);
+    launch_kernel(attn_bias_decode_kernel<W, EXACT>, dim3(p.S, p.G, p.splits), dim3(nw * 32), smem, stream, p);
     if (p.splits > 1) launch_kernel(attn_bias_merge_kernel, dim3(p.S, p.G, (p.H / p.G * p.dv + 127) / 128), dim3(128), 0, stream, p);
     return launch_status();
 }
 
-template <int W>
+template <int W, bool EXACT>
 int launch_attn_bias(const BiasAttnParams& p, int num_tiles, cudaStream_t stream) {
     const int E = p.dk + p.dv;
     const int g = p.H / p.G;
@@ -553,11 +574,11 @@ int launch_attn_bias(const BiasAttnParams& p, int num_tiles, cudaStream_t stream
                         + static_cast<size_t>(g) * 2 * bias_row_floats(kBiasTileRows / g) * sizeof(float);
     static bool raised = false;
     if (!raised) {
-        if (cudaFuncSetAttribute(attn_bias_kernel<W>, cudaFuncAttributeMaxDynamicSharedMemorySize, 136 * 1024) != cudaSuccess)
+        if (cudaFuncSetAttribute(attn_bias_kernel<W, EXACT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 136 * 1024) != cudaSuccess)
             return launch_status();
         raised = true;
     }
-    launch_kernel(attn_bias_kernel<W>, dim3(num_tiles, p.G), dim3(kBiasThreads), smem, stream, p);
+    launch_kernel(attn_bias_kernel<W, EXACT>, dim3(num_tiles, p.G), dim3(kBiasThreads), smem, stream, p);
     return launch_status();
 }
 
@@ -603,14 +624,16 @@ extern "C" int cvb_attn_bias_bf16(void* out, const void* q, int q_stride, const 
         p.splits = splits; p.parts = parts;
     }
     const int w = dk > dv ? dk : dv;
-    if (decode) {
-        if (w <= 32) return launch_attn_bias_decode<32>(p, stream);
-        if (w <= 64) return launch_attn_bias_decode<64>(p, stream);
-        if (w <= 96) return launch_attn_bias_decode<96>(p, stream);
-        return launch_attn_bias_decode<128>(p, stream);
+    const bool exact = dk == dv && (dk == 32 || dk == 64 || dk == 96 || dk == 128);
+#define CVB_BIAS_WIDTH(WW)                                                                                               \
+    if (w <= WW) {                                                                                                       \
+        if (decode) return exact ? launch_attn_bias_decode<WW, true>(p, stream) : launch_attn_bias_decode<WW, false>(p, stream); \
+        return exact ? launch_attn_bias<WW, true>(p, num_tiles, stream) : launch_attn_bias<WW, false>(p, num_tiles, stream);     \
     }
-    if (w <= 32) return launch_attn_bias<32>(p, num_tiles, stream);
-    if (w <= 64) return launch_attn_bias<64>(p, num_tiles, stream);
-    if (w <= 96) return launch_attn_bias<96>(p, num_tiles, stream);
-    return launch_attn_bias<128>(p, num_tiles, stream);
+    CVB_BIAS_WIDTH(32)
+    CVB_BIAS_WIDTH(64)
+    CVB_BIAS_WIDTH(96)
+    CVB_BIAS_WIDTH(128)
+#undef CVB_BIAS_WIDTH
+    return CVB_E_UNSUPPORTED;
 }
