@@ -111,6 +111,45 @@ def write_model(path, cfg, seed, sharpen=4.0):
     return path
 
 
+def random_config(seed, tensor_core=False):
+    """A configuration drawn at random: 2 to 6 layers of both kinds in any order, with no, a dense or a routed feed-forward;
+    sizes odd, prime, 1 or large; layers that read an earlier layer's keys and values.  With `tensor_core` the key and value
+    sizes of attention are multiples of 16, the sizes its tensor-core kernels take."""
+    import random
+    r = random.Random(1000 + seed)
+    width = r.choice([32, 40, 50, 64, 72, 100, 128])
+    layers, writers = [], []
+    for i in range(r.randint(2, 6)):
+        if r.random() < 0.6:
+            if writers and r.random() < 0.4:
+                j = r.choice(writers)
+                m = dict(layers[j]["mixer"], kv_from=j, scale=r.choice([0.1, 0.2, 0.35]), bias_max=r.randint(layers[j]["mixer"]["bias_rows"] // 2 + 1, 260))
+                m["q_temp"] = {"coef": r.choice([0.0, 0.2, 0.7]), "every": r.choice([1, 3, 16, 50])}
+                layer = {"type": "attention", "mixer": m}
+            else:
+                kv, group = r.choice([1, 2, 3]), r.choice([1, 2, 4, 5] if not tensor_core else [1, 2, 4, 8])
+                sizes = [16, 32, 48, 64, 96, 128] if tensor_core else [6, 8, 10, 16, 24, 40, 64]
+                rows = r.choice([4, 6, 8, 12, 20, 32])
+                layer = _attn(kv * group, kv, r.choice(sizes), r.choice(sizes), rows, r.randint(rows // 2 + 1, 260),
+                              r.choice([0.0, 0.2, 0.7]), r.choice([1, 3, 16, 50]), r.choice([0.1, 0.2, 0.35]))
+                writers.append(i)
+        else:
+            kv, group = r.choice([1, 2]), r.choice([1, 2, 3])
+            layer = _delta(kv * group, kv, r.choice([3, 8, 16, 33, 64]), r.choice([5, 8, 16, 40, 64]), r.randint(1, 5))
+        kind = r.random()
+        if kind < 0.2:
+            mlp = None
+        elif kind < 0.55:
+            mlp = _dense(r.choice([24, 50, 64, 128]), r.choice([0.5, 1.0, 2.5, 7.0]))
+        else:
+            experts = r.randint(2, 9)
+            mlp = _moe(experts, r.randint(1, experts), r.choice([8, 20, 32, 64]), r.choice([0.5, 1.0, 2.0, 3.5]),
+                       shared=r.choice([0, 8, 24, 48]))
+        layers.append(_layer(layer, mlp))
+    return {"architecture": "Lorulix", "vocab": r.randint(40, 300), "width": width, "max_positions": 256,
+            "norm": {"eps": r.choice([1e-6, 1e-5, 1e-4])}, "canon": {"taps": r.randint(1, 5)}, "layers": layers}
+
+
 def write_all(base):
     return {name: write_model(os.path.join(base, name), cfg, seed) for name, (cfg, seed, _) in SETUPS.items()}
 

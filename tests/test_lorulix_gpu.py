@@ -75,6 +75,34 @@ def test_whole_tail_and_portions_match_the_plain_implementation(lx_dirs, name, d
     assert all(runner.cache.num_free_pages(g) == 128 // lm.page_size(name) for g in range(len(runner.group_specs)))
 
 
+@pytest.mark.parametrize("seed,dtype", [(s, "float32") for s in range(8)] + [(s, "bfloat16") for s in (9, 13, 14, 17, 19, 22)])
+def test_configurations_drawn_at_random(tmp_path, seed, dtype):
+    """Layers of both kinds in any order and size (tests/lorulix_models.py: random_config): a whole prompt, a tail decoded
+    token by token, portions down to two tokens and three unequal requests in one batch.  In float32 nothing but the order
+    of sums may differ; in bfloat16 the sizes are the ones the tensor-core kernels take, and the seeds are those whose models
+    do not amplify 16-bit rounding beyond the tolerance (the plain implementation with 16-bit rounding stays within it; a
+    delta rule over unit vectors of three elements behind sharpened convolutions, for one, does not)."""
+    import random
+    cfg = lm.random_config(seed, tensor_core=dtype == "bfloat16")
+    d = lm.write_model(str(tmp_path / "m"), cfg, seed)
+    toks = {"w": lm.clear_tokens(d, 150, 1), "t": lm.clear_tokens(d, 140, 2), "p": lm.clear_tokens(d, 150, 1),
+            "x": lm.clear_tokens(d, 70, 5), "y": lm.clear_tokens(d, 33, 6), "z": lm.clear_tokens(d, 2, 7)}
+    tb = TraceBuilder()
+    whole(tb, "w", toks["w"])
+    tail_one_by_one(tb, "t", toks["t"], tail=40)
+    portions(tb, "p", toks["p"])
+    tb.add([("x", toks["x"][:37], range(37)), ("y", toks["y"][:32], range(32)), ("z", toks["z"][:1], [0])])
+    tb.add([("x", toks["x"][37:39], range(2)), ("y", toks["y"][32:], [0]), ("z", toks["z"][1:], [0])], end=["y", "z"])
+    tb.add([("x", toks["x"][39:], range(31))], end=["x"])
+    from cppvllm_b200.engine.runner import ModelRunner
+    page = random.Random(seed).choice([16, 32, 64])
+    runner = ModelRunner(d, dtype=torch.float32 if dtype == "float32" else torch.bfloat16, page_size=page, num_pages=256 // page,
+                         max_step_tokens=256, max_seqs=4, max_model_len=256, num_state_slots=3)
+    rows = rows_by_position(tb.steps, run_trace_in_process(runner, tb.steps))
+    assert len(rows) == 150 + 140 + 150 + 70 + 33 + 2
+    check(rows, refs_of(d, toks), dtype)
+
+
 @pytest.mark.parametrize("dtype,eager", [("float32", False), ("bfloat16", False), ("float32", True)])
 @pytest.mark.parametrize("name", ["lx_a", "lx_b", "lx_c"])
 def test_unequal_requests_in_one_batch_with_pages_and_slots_used_again(lx_dirs, name, dtype, eager):
