@@ -40,19 +40,36 @@ route_topk_kernel(int* __restrict__ ids, float* __restrict__ weights, const T* _
     if (t >= n_tokens) return;
     float* z = smem + warp * E;
     const T* xr = x + t * D;
-    for (int e = 0; e < E; ++e) {
-        const float* w = wr + static_cast<int64_t>(e) * D;
-        float d = 0.f;
-        for (int i = lane; i < D; i += 32) d = fmaf(to_float(xr[i]), w[i], d);
-        d = warp_sum(d);
-        if (lane == 0) z[e] = d + (bias ? bias[e] : 0.f);
-    }
-    for (int e = 0; e < extra; ++e) {
-        const float* w = wr + static_cast<int64_t>(E + e) * D;
-        float d = 0.f;
-        for (int i = lane; i < D; i += 32) d = fmaf(to_float(xr[i]), w[i], d);
-        d = warp_sum(d);
-        if (lane == 0) extra_out[t * extra + e] = d;
+    // four rows of Wr at a time, each with a sum of its own (a row's sum runs over the same elements in the same order as
+    // alone): four independent loads in flight per lane and step instead of one chain
+    for (int e0 = 0; e0 < E + extra; e0 += 4) {
+        const int ne = min(4, E + extra - e0);
+        const float* w = wr + static_cast<int64_t>(e0) * D;
+        float d[4] = {0.f, 0.f, 0.f, 0.f};
+        if (ne == 4) {
+            for (int i = lane; i < D; i += 32) {
+                const float xv = to_float(xr[i]);
+#pragma unroll
+                for (int q = 0; q < 4; ++q) d[q] = fmaf(xv, w[static_cast<int64_t>(q) * D + i], d[q]);
+            }
+        } else {
+            for (int i = lane; i < D; i += 32) {
+                const float xv = to_float(xr[i]);
+#pragma unroll
+                for (int q = 0; q < 4; ++q)
+                    if (q < ne) d[q] = fmaf(xv, w[static_cast<int64_t>(q) * D + i], d[q]);
+            }
+        }
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            if (q >= ne) break;
+            const float v = warp_sum(d[q]);
+            const int e = e0 + q;
+            if (lane == 0) {
+                if (e < E) z[e] = v + (bias ? bias[e] : 0.f);
+                else extra_out[t * extra + (e - E)] = v;
+            }
+        }
     }
     __syncwarp();
     float all = 0.f;                                    // mode 1: the sum over all experts, against the largest logit

@@ -358,15 +358,15 @@ def _sandwich_lib():
 
 def input_conv(out: torch.Tensor, a: torch.Tensor, taps: torch.Tensor, state: torch.Tensor, hist_off: int, seq_of_token, cu_seqlens,
                state_slots) -> torch.Tensor:
-    """out[t, c] = a[t, c] + sum_j taps[c, j] * a[t - K + 1 + j, c]: a causal convolution over time per channel, added to its
-    input.  What lies before the step's portion comes from the request's history: K - 1 rows of D floats from `hist_off` on in
+    """out[t, c] = a[t, c] + sum_j taps[j, c] * a[t - K + 1 + j, c]: a causal convolution over time per channel, added to its
+    input; `taps` holds one row of D weights per tap, the oldest tap first.  What lies before the step's portion comes from the request's history: K - 1 rows of D floats from `hist_off` on in
     the request's state row (oldest first)."""
     _cuda(out, a, taps, state, seq_of_token, cu_seqlens, state_slots); _contig(out, a, taps, seq_of_token, cu_seqlens, state_slots)
     sp, sf, n_slots = _state_args(state)
     T, D = a.shape
-    if out.shape != a.shape or out.dtype != a.dtype or taps.dtype != torch.float32 or taps.dim() != 2 or taps.shape[0] != D:
-        raise KernelError("input_conv: out like a [T, D]; taps float32 [D, K]")
-    _check(_sandwich_lib().cvb_input_conv(_ptr(out), _ptr(a), _ptr(taps), c_int(T), c_int(D), c_int(taps.shape[1]), sp, sf,
+    if out.shape != a.shape or out.dtype != a.dtype or taps.dtype != torch.float32 or taps.dim() != 2 or taps.shape[1] != D:
+        raise KernelError("input_conv: out like a [T, D]; taps float32 [K, D]")
+    _check(_sandwich_lib().cvb_input_conv(_ptr(out), _ptr(a), _ptr(taps), c_int(T), c_int(D), c_int(taps.shape[0]), sp, sf,
                                           c_int64(hist_off), _ptr(seq_of_token), _ptr(cu_seqlens), _ptr(state_slots), c_int(n_slots),
                                           c_int(dtype_code(a.dtype)), _ptr(error_flag(a.device)), _stream()), "input_conv")
     return out

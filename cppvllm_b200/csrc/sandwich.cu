@@ -2,8 +2,8 @@
 // input through a short causal convolution and leave through a learned gate; and what stands around attention with a norm
 // over the whole query and key projections.  The residual stream is float; T is the activations' element type.
 //
-//   input_conv      : out[t, c] = T( a[t, c] + sum_j w[c, j] * a[t - K + 1 + j, c] ): a causal convolution over time on each
-//                     channel, added to its own input.  Tokens before the portion come from the request's history (the last
+//   input_conv      : out[t, c] = T( a[t, c] + sum_j w[j, c] * a[t - K + 1 + j, c] ): a causal convolution over time on each
+//                     channel, added to its own input (w holds one row of D weights per tap, the oldest tap first).  Tokens before the portion come from the request's history (the last
 //                     K - 1 inputs of its earlier portions, zero at admission), which lies in the request's state row.
 //   gated_norm_add  : v = y * sigmoid(z + b);  h[t, :] += v / sqrt(mean(v^2) + eps) * w   (the sublayer's output through its gate,
 //                     the norm behind the sublayer, the sum into the stream: one kernel).  With a second weight w2 it also
@@ -46,9 +46,58 @@ input_conv_kernel(T* __restrict__ out, const T* __restrict__ a, const float* __r
         for (int j = 0; j < taps; ++j) {
             const int o = local - (taps - 1) + j;
             const float x = o >= 0 ? to_float(a[(t - (taps - 1) + j) * D + c]) : hist[static_cast<int64_t>(local + j) * D + c];
-            acc = fmaf(w[static_cast<int64_t>(c) * taps + j], x, acc);
+            acc = fmaf(w[static_cast<int64_t>(j) * D + c], x, acc);
         }
         out[t * D + c] = from_float<T>(to_float(a[t * D + c]) + acc);
+    }
+}
+
+// the same with 16 bytes of a row per thread (D a multiple of the chunk, rows on 16-byte boundaries); a channel's sum runs over
+// the taps in the same order as above
+template <typename T>
+__global__ void __launch_bounds__(kSandThreads)
+input_conv_vec_kernel(T* __restrict__ out, const T* __restrict__ a, const float* __restrict__ w, int D, int taps,
+                      const float* __restrict__ state, int64_t state_floats, int64_t hist_off, const int* __restrict__ seq_of_token,
+                      const int* __restrict__ cu_seqlens, const int* __restrict__ state_slots, int num_slots, int* __restrict__ err) {
+    pdl_trigger();
+    pdl_wait();
+    constexpr int N = 16 / sizeof(T);
+    const int64_t t = blockIdx.x;
+    const int s = seq_of_token[t];
+    const int local = static_cast<int>(t) - cu_seqlens[s];
+    const int slot = state_slots[s];
+    if (slot < 0 || slot >= num_slots) {
+        if (threadIdx.x == 0) atomicExch(err, 2);
+        return;
+    }
+    const float* hist = state + static_cast<int64_t>(slot) * state_floats + hist_off;
+    for (int c = threadIdx.x * N; c < D; c += kSandThreads * N) {
+        float acc[N], x[N];
+#pragma unroll
+        for (int i = 0; i < N; ++i) acc[i] = 0.f;
+        for (int j = 0; j < taps; ++j) {
+            const int o = local - (taps - 1) + j;
+            if (o >= 0) {
+                alignas(16) T v[N];
+                *reinterpret_cast<uint4*>(v) = *reinterpret_cast<const uint4*>(a + (t - (taps - 1) + j) * D + c);
+#pragma unroll
+                for (int i = 0; i < N; ++i) x[i] = to_float(v[i]);
+            } else {
+                const float* hp = hist + static_cast<int64_t>(local + j) * D + c;
+#pragma unroll
+                for (int i = 0; i < N; ++i) x[i] = hp[i];
+            }
+            alignas(16) float wj[N];
+#pragma unroll
+            for (int i = 0; i < N; i += 4)
+                *reinterpret_cast<float4*>(wj + i) = *reinterpret_cast<const float4*>(w + static_cast<int64_t>(j) * D + c + i);
+#pragma unroll
+            for (int i = 0; i < N; ++i) acc[i] = fmaf(wj[i], x[i], acc[i]);
+        }
+        alignas(16) T y[N];                               // x holds the token's own row: the last tap's
+#pragma unroll
+        for (int i = 0; i < N; ++i) y[i] = from_float<T>(x[i] + acc[i]);
+        *reinterpret_cast<uint4*>(out + t * D + c) = *reinterpret_cast<const uint4*>(y);
     }
 }
 
@@ -207,8 +256,14 @@ extern "C" int cvb_input_conv(void* out, const void* a, const float* w, int T, i
     if (T == 0) return CVB_OK;
     if (T < 0 || D <= 0 || taps <= 0 || num_slots <= 0) return CVB_E_SIZE;
     if (hist_off < 0 || state_floats < hist_off + static_cast<int64_t>(taps - 1) * D) return CVB_E_SHAPE;
-#define CALL(TY) launch_kernel(input_conv_kernel<TY>, dim3(T), dim3(kSandThreads), 0, stream, (TY*)out, (const TY*)a, w, D, taps, state, \
-                               state_floats, hist_off, seq_of_token, cu_seqlens, state_slots, num_slots, err_flag)
+    const bool aligned = ((reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(w)) & 15) == 0;
+#define CALL(TY)                                                                                                                          \
+    if (aligned && D % (16 / (int)sizeof(TY)) == 0)                                                                                       \
+        launch_kernel(input_conv_vec_kernel<TY>, dim3(T), dim3(kSandThreads), 0, stream, (TY*)out, (const TY*)a, w, D, taps, state,       \
+                      state_floats, hist_off, seq_of_token, cu_seqlens, state_slots, num_slots, err_flag);                                \
+    else                                                                                                                                  \
+        launch_kernel(input_conv_kernel<TY>, dim3(T), dim3(kSandThreads), 0, stream, (TY*)out, (const TY*)a, w, D, taps, state,           \
+                      state_floats, hist_off, seq_of_token, cu_seqlens, state_slots, num_slots, err_flag)
     CVB_DISPATCH_DTYPE(dtype, CALL);
 #undef CALL
     return launch_status();

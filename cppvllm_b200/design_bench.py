@@ -594,7 +594,7 @@ def lorulix_kernel_pairs(s, pk):
     # -- the block: input convolution, and the kernel that closes a sublayer ---------------------------------------------------
     a16, x16, yy, zz, nxt = rnd(T, D), torch.empty(T, D, dtype=bf, device=d), rnd(T, D), rnd(T, D), torch.empty(T, D, dtype=bf, device=d)
     h32 = torch.randn(T, D, generator=g, device=d)
-    taps = rnd(D, 4, dtype=f32)
+    taps = rnd(4, D, dtype=f32)
     hist = torch.zeros(2, 3 * D, dtype=f32, device=d)
     new = _us(lambda i: ops.input_conv(x16, a16, taps, hist, 0, seq_of, cu, slots1))
     alone("input_convolution_2048_tokens", new, T * D * 4.0)

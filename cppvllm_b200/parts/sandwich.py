@@ -73,10 +73,11 @@ class SandwichBlock(Block):
 
     def bind(self, tensors) -> None:
         t = lambda n: tensors[self.full_name(n)]          # noqa: E731
-        self.taps1, self.w_g1, self.b_g1 = t("canon1").contiguous(), t("rg1"), t("rg1.b")
+        # the convolution's weights by tap ([taps, D], oldest first): a tap's weights of neighbouring channels lie side by side
+        self.taps1, self.w_g1, self.b_g1 = t("canon1").float().t().contiguous(), t("rg1"), t("rg1.b")
         self.w_out1 = (t("norm1b") + self.out_offset).contiguous()
         if self.ffn is not None:
-            self.taps2, self.w_g2, self.b_g2 = t("canon2").contiguous(), t("rg2"), t("rg2.b")
+            self.taps2, self.w_g2, self.b_g2 = t("canon2").float().t().contiguous(), t("rg2"), t("rg2.b")
             self.w_out2 = (t("norm2b") + self.out_offset).contiguous()
 
     def weight_bytes(self) -> int:

@@ -77,7 +77,7 @@ def test_a_sublayer_between_its_convolution_and_its_closing_kernel(dtype, D, K):
                 a_rows.append(a[at[r]:at[r] + n]); z_rows.append(z[at[r]:at[r] + n]); h_rows.append(h[at[r]:at[r] + n]); at[r] += n
                 cu.append(cu[-1] + n); slots.append(slot_of[r]); seq_of += [i] * n
             a, z, h = _dev(torch.cat(a_rows)), _dev(torch.cat(z_rows)), _dev(torch.cat(h_rows))
-            x = ops.input_conv(torch.empty_like(a), a, _dev(taps), state, front, _i32(seq_of), _i32(cu), _i32(slots))
+            x = ops.input_conv(torch.empty_like(a), a, _dev(taps.t().contiguous()), state, front, _i32(seq_of), _i32(cu), _i32(slots))
             y = (x.float() * 2).to(dtype)
             nxt = torch.empty_like(a)
             ops.gated_norm_add(h, y, _dev(w_out), eps, gate=z, gate_bias=_dev(bias), next_weight=_dev(w_next), next_eps=eps, next_out=nxt,
