@@ -44,6 +44,8 @@ LIBRARIES: Dict[str, List[str]] = {
     "latent": ["latent.cu"],
     "recurrent": ["recurrent.cu"],
     "sandwich": ["sandwich.cu"],
+    "hyper": ["hyper.cu"],
+    "attn_masked": ["attention_masked.cu"],
     # host code only (the cache manager and the scheduler); nvcc hands it to the host compiler
     "runtime": ["cache_runtime.cpp", "scheduler_runtime.cpp"],
 }

@@ -10,7 +10,8 @@
 //                      (the unrotated query taken through the key up-projection, laid out [head, token, rank]) comes from a
 //                      batched product and q_rot is the head's positional part inside the packed query projection.
 //   head_gate        : att[t, h, :] = T( o[h, t, :] * sigmoid(g[t, h]) ): one gate per token and head, and the move from the
-//                      batched product's [head, token, :] to rows of concatenated heads.
+//                      batched product's [head, token, :] to rows of concatenated heads.  With `per_element` the gate has
+//                      one number per element of the concatenated heads: att[t, i] = T( o[..] * sigmoid(g[t, i]) ).
 //
 // The rotation pairs element 2i with element 2i+1 of the first `rot` elements (cos and sin tables [positions, rot / 2],
 // float); elements behind them pass unchanged.  Norm statistics and the rotation are float.
@@ -101,13 +102,14 @@ latent_q_assemble_kernel(T* __restrict__ q_out, const T* __restrict__ q_abs, con
 
 template <typename T>
 __global__ void __launch_bounds__(kLatentThreads)
-head_gate_kernel(T* __restrict__ out, const T* __restrict__ o, const T* __restrict__ gate, int gate_stride, int H, int vd, int T_total) {
+head_gate_kernel(T* __restrict__ out, const T* __restrict__ o, const T* __restrict__ gate, int gate_stride, int H, int vd, int T_total,
+                 int per_element) {
     pdl_trigger();
     pdl_wait();
     const int64_t t = blockIdx.x;
     for (int i = blockIdx.y * kLatentThreads + threadIdx.x; i < H * vd; i += gridDim.y * kLatentThreads) {
         const int h = i / vd, j = i - h * vd;
-        const float z = to_float(gate[t * gate_stride + h]);
+        const float z = to_float(gate[t * gate_stride + (per_element ? i : h)]);
         out[t * H * vd + i] = from_float<T>(to_float(o[(static_cast<int64_t>(h) * T_total + t) * vd + j]) * (1.f / (1.f + expf(-z))));
     }
 }
@@ -148,13 +150,13 @@ extern "C" int cvb_latent_q_assemble(void* q_out, const void* q_abs, const void*
     return launch_status();
 }
 
-extern "C" int cvb_head_gate(void* out, const void* o, const void* gate, int T, int gate_stride, int H, int vd, int dtype,
-                             cudaStream_t stream) {
+extern "C" int cvb_head_gate(void* out, const void* o, const void* gate, int T, int gate_stride, int H, int vd, int per_element,
+                             int dtype, cudaStream_t stream) {
     if (T == 0) return CVB_OK;
-    if (T < 0 || H <= 0 || vd <= 0 || gate_stride < H) return CVB_E_SIZE;
+    if (T < 0 || H <= 0 || vd <= 0 || gate_stride < (per_element ? H * vd : H)) return CVB_E_SIZE;
     const int per_row = (H * vd + kLatentThreads - 1) / kLatentThreads;
 #define CALL(TY) launch_kernel(head_gate_kernel<TY>, dim3(T, per_row < 64 ? per_row : 64), dim3(kLatentThreads), 0, stream, (TY*)out, (const TY*)o, (const TY*)gate, \
-                               gate_stride, H, vd, T)
+                               gate_stride, H, vd, T, per_element)
     CVB_DISPATCH_DTYPE(dtype, CALL);
 #undef CALL
     return launch_status();

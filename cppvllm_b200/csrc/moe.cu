@@ -6,6 +6,8 @@
 //                    `mode` 1: weights scale * exp(z_e) / sum over ALL experts of exp(z_c) instead (not renormalised over the
 //                    winners).  Rows of Wr behind the E experts' (`extra` of them) are not experts: their raw products
 //                    leave as extra_out[t, :] (a gate per token that shares the router's pass over x).
+//                    `mode` 2: weights sigmoid(z_e) of the winners, each on its own (no sum over experts at all).
+//   With `on_input` = 1 a pair's weight multiplies the expert's INPUT instead of its output: y[t] = sum_k expert_e(T(w_k x[t])).
 //   With `gated` = 0 an expert is  Wd_e ( T(relu(T(Wu_e x))^2) )  and Wgu holds [E, ff, D].
 //   An expert is  Wd_e ( T(act(Wg_e x) * (Wu_e x)) ),  act(z) = z * sigmoid(z);  the layer's output is
 //   y[t] = T( sum_k weights[t, k] * expert_{ids[t, k]}(x[t]) ).  Wgu is [E, 2 ff, D] (gate rows over up rows), Wd is
@@ -95,7 +97,7 @@ route_topk_kernel(int* __restrict__ ids, float* __restrict__ weights, const T* _
             if (ob > best || (ob == best && oa < at)) { best = ob; at = oa; }
         }
         if (k == 0) z_first = best;
-        const float p = expf(best - z_first);
+        const float p = mode == 2 ? best : expf(best - z_first);      // mode 2 keeps the logit itself
         sum += p;
         if (lane == 0) {
             ids[t * top + k] = at;
@@ -103,6 +105,10 @@ route_topk_kernel(int* __restrict__ ids, float* __restrict__ weights, const T* _
             z[at] = -INFINITY;
         }
         __syncwarp();
+    }
+    if (mode == 2) {                                    // the winners' own logistic scores
+        for (int k = lane; k < top; k += 32) weights[t * top + k] = scale / (1.f + expf(-weights[t * top + k]));
+        return;
     }
     const float inv = mode == 1 ? scale / all : 1.f / sum;
     for (int k = lane; k < top; k += 32) weights[t * top + k] *= inv;     // lane 0's writes are visible after the syncwarp
@@ -139,7 +145,8 @@ template <> __device__ __forceinline__ float dot8_of<__nv_bfloat16>(const __nv_b
 template <typename T>
 __global__ void __launch_bounds__(kExpertThreads)
 expert_hidden_kernel(T* __restrict__ hid, const T* __restrict__ x, const int* __restrict__ ids, const T* __restrict__ wgu,
-                     int D, int F, int E, int top, int per_block, int gated, int* __restrict__ err) {
+                     int D, int F, int E, int top, int per_block, int gated, const float* __restrict__ in_weights,
+                     int* __restrict__ err) {
     pdl_trigger();
     pdl_wait();
     extern __shared__ __align__(16) float smem[];
@@ -152,7 +159,12 @@ expert_hidden_kernel(T* __restrict__ hid, const T* __restrict__ x, const int* __
         if (threadIdx.x == 0) atomicExch(err, 7);
         e = 0;
     }
-    for (int i = threadIdx.x; i < D; i += kExpertThreads) xs[i] = to_float(x[t * D + i]);
+    const float wi = in_weights != nullptr ? in_weights[pair] : 1.f;
+    if (in_weights != nullptr) {
+        for (int i = threadIdx.x; i < D; i += kExpertThreads) xs[i] = rnd<T>(wi * to_float(x[t * D + i]));
+    } else {
+        for (int i = threadIdx.x; i < D; i += kExpertThreads) xs[i] = to_float(x[t * D + i]);
+    }
     __syncthreads();
     const T* g_rows = wgu + static_cast<int64_t>(e) * (gated ? 2 : 1) * F * D;
     const T* u_rows = g_rows + static_cast<int64_t>(F) * D;
@@ -187,7 +199,7 @@ expert_hidden_kernel(T* __restrict__ hid, const T* __restrict__ x, const int* __
 template <typename T>
 __global__ void __launch_bounds__(kExpertThreads)
 expert_down_kernel(T* __restrict__ y, const T* __restrict__ hid, const int* __restrict__ ids, const float* __restrict__ weights,
-                   const T* __restrict__ wd, int D, int F, int E, int top, int per_block) {
+                   const T* __restrict__ wd, int D, int F, int E, int top, int per_block, int on_input) {
     pdl_trigger();
     pdl_wait();
     extern __shared__ __align__(16) float smem[];
@@ -201,7 +213,7 @@ expert_down_kernel(T* __restrict__ y, const T* __restrict__ hid, const int* __re
     for (int k = 0; k < top; ++k) {
         int e = ids[t * top + k];
         if (e < 0 || e >= E) e = 0;                      // reported by the kernel in front
-        const float wk = weights[t * top + k];
+        const float wk = on_input ? 1.f : weights[t * top + k];
         __syncthreads();
         for (int i = threadIdx.x; i < F; i += kExpertThreads) hs[i] = to_float(hid[(t * top + k) * F + i]);
         __syncthreads();
@@ -278,7 +290,20 @@ sort_pairs_padded_kernel(int* __restrict__ tile_expert, int* __restrict__ row_to
     }
 }
 
-// y[t, :] = sum_k weights[t, k] * rows[slot_of[t * top + k], :]
+// xs[slot_of[pair], :] = T(weights[pair] * x[pair / top, :]): the rows of the grouped product when a pair's weight multiplies
+// the expert's input.  Padding rows keep what they held; they are computed and never read.
+__global__ void scatter_pairs_scaled_kernel(__nv_bfloat16* __restrict__ xs, const __nv_bfloat16* __restrict__ x,
+                                            const int* __restrict__ slot_of, const float* __restrict__ weights, int D, int top) {
+    pdl_trigger();
+    pdl_wait();
+    const int64_t pair = blockIdx.x;
+    const float w = weights[pair];
+    const __nv_bfloat16* src = x + pair / top * D;
+    __nv_bfloat16* dst = xs + static_cast<int64_t>(slot_of[pair]) * D;
+    for (int d = threadIdx.x; d < D; d += blockDim.x) dst[d] = __float2bfloat16_rn(w * __bfloat162float(src[d]));
+}
+
+// y[t, :] = sum_k weights[t, k] * rows[slot_of[t * top + k], :]   (weights = nullptr: all 1)
 __global__ void combine_pairs_kernel(__nv_bfloat16* __restrict__ y, const __nv_bfloat16* __restrict__ rows, const int* __restrict__ slot_of,
                                      const float* __restrict__ weights, int D, int top) {
     pdl_trigger();
@@ -287,7 +312,7 @@ __global__ void combine_pairs_kernel(__nv_bfloat16* __restrict__ y, const __nv_b
     for (int d = threadIdx.x; d < D; d += blockDim.x) {
         float s = 0.f;
         for (int k = 0; k < top; ++k)
-            s = fmaf(weights[t * top + k], __bfloat162float(rows[static_cast<int64_t>(slot_of[t * top + k]) * D + d]), s);
+            s = fmaf(weights != nullptr ? weights[t * top + k] : 1.f, __bfloat162float(rows[static_cast<int64_t>(slot_of[t * top + k]) * D + d]), s);
         y[t * D + d] = __float2bfloat16_rn(s);
     }
 }
@@ -300,7 +325,7 @@ extern "C" int cvb_route_topk(int* ids, float* weights, const void* x, const flo
                               int top, int mode, float scale, int extra, float* extra_out, int dtype, cudaStream_t stream) {
     if (T == 0) return CVB_OK;
     if (T < 0 || D <= 0 || E <= 0 || top <= 0 || extra < 0 || (extra > 0 && extra_out == nullptr)) return CVB_E_SIZE;
-    if (mode != 0 && mode != 1) return CVB_E_SHAPE;
+    if (mode < 0 || mode > 2) return CVB_E_SHAPE;
     if (top > E || E > 2048) return CVB_E_SHAPE;
     const size_t smem = static_cast<size_t>(kRouteWarps) * E * sizeof(float);
 #define CALL(TY) launch_kernel(route_topk_kernel<TY>, dim3((T + kRouteWarps - 1) / kRouteWarps), dim3(kRouteWarps * 32), smem, \
@@ -311,7 +336,7 @@ extern "C" int cvb_route_topk(int* ids, float* weights, const void* x, const flo
 }
 
 extern "C" int cvb_expert_rows(void* y, void* hid, const void* x, const int* ids, const float* weights, const void* wgu,
-                               const void* wd, int T, int D, int F, int E, int top, int gated, int dtype, int* err_flag,
+                               const void* wd, int T, int D, int F, int E, int top, int gated, int on_input, int dtype, int* err_flag,
                                cudaStream_t stream) {
     if (T == 0) return CVB_OK;
     if (T < 0 || D <= 0 || F <= 0 || E <= 0 || top <= 0) return CVB_E_SIZE;
@@ -332,9 +357,9 @@ extern "C" int cvb_expert_rows(void* y, void* hid, const void* x, const int* ids
         if (smem2 > 48 * 1024)                                                                                           \
             cudaFuncSetAttribute(expert_down_kernel<TY>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem2);       \
         launch_kernel(expert_hidden_kernel<TY>, dim3((unsigned)pairs, (F + f_per - 1) / f_per), dim3(kExpertThreads), smem1,  \
-                      stream, (TY*)hid, (const TY*)x, ids, (const TY*)wgu, D, F, E, top, f_per, gated, err_flag);                \
+                      stream, (TY*)hid, (const TY*)x, ids, (const TY*)wgu, D, F, E, top, f_per, gated, on_input ? weights : nullptr, err_flag);                \
         launch_kernel(expert_down_kernel<TY>, dim3(T, (D + d_per - 1) / d_per), dim3(kExpertThreads), smem2, stream,      \
-                      (TY*)y, (const TY*)hid, ids, weights, (const TY*)wd, D, F, E, top, d_per);                          \
+                      (TY*)y, (const TY*)hid, ids, weights, (const TY*)wd, D, F, E, top, d_per, on_input);                          \
     } while (0)
     CVB_DISPATCH_DTYPE(dtype, CALL);
 #undef CALL
@@ -349,6 +374,14 @@ extern "C" int cvb_sort_pairs_padded(int* tile_expert, int* row_token, int* slot
     if (pairs > (1 << 30) || (pairs + 127) / 128 + E > max_tiles) return CVB_E_SCRATCH;
     launch_kernel(sort_pairs_padded_kernel, dim3(1), dim3(kSortThreads), (2 * static_cast<size_t>(E) + 1) * sizeof(int), stream,
                   tile_expert, row_token, slot_of, ids, static_cast<int>(pairs), E, top, 128, max_tiles, err_flag);
+    return launch_status();
+}
+
+extern "C" int cvb_scatter_pairs_scaled_bf16(void* xs, const void* x, const int* slot_of, const float* weights, int T, int D, int top,
+                                             cudaStream_t stream) {
+    if (T <= 0 || D <= 0 || top <= 0) return CVB_E_SIZE;
+    launch_kernel(scatter_pairs_scaled_kernel, dim3(static_cast<unsigned>(T) * top), dim3(D >= 1024 ? 256 : 128), 0, stream,
+                  (__nv_bfloat16*)xs, (const __nv_bfloat16*)x, slot_of, weights, D, top);
     return launch_status();
 }
 

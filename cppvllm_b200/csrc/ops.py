@@ -580,15 +580,17 @@ def latent_q_assemble(q_out: torch.Tensor, q_abs: torch.Tensor, q: torch.Tensor,
     return q_out
 
 
-def head_gate(out: torch.Tensor, o: torch.Tensor, gate: torch.Tensor, num_heads: int, vdim: int) -> torch.Tensor:
-    """out[t, h * vdim + j] = o[h, t, j] * sigmoid(gate[t, h]); gate is a view of H columns inside rows of gate.stride(0)."""
+def head_gate(out: torch.Tensor, o: torch.Tensor, gate: torch.Tensor, num_heads: int, vdim: int, per_element: bool = False) -> torch.Tensor:
+    """out[t, h * vdim + j] = o[h, t, j] * sigmoid(gate[t, h]); gate is a view of H columns inside rows of gate.stride(0).
+    `per_element`: the gate has H * vdim columns, one per element: out[t, i] = o[..] * sigmoid(gate[t, i])."""
     _cuda(out, o, gate); _contig(out, o)
     T = out.shape[0]
+    cols = num_heads * vdim if per_element else num_heads
     if (out.dtype != o.dtype or gate.dtype != o.dtype or out.shape[1] != num_heads * vdim or o.numel() != T * num_heads * vdim
-            or gate.shape != (T, num_heads) or gate.stride(1) != 1):
-        raise KernelError("head_gate: o [H, T, vdim], out [T, H * vdim], gate [T, H] of one element type")
+            or gate.shape != (T, cols) or gate.stride(1) != 1):
+        raise KernelError("head_gate: o [H, T, vdim], out [T, H * vdim], gate [T, H] (or [T, H * vdim]) of one element type")
     _check(_latent_lib().cvb_head_gate(_ptr(out), _ptr(o), _ptr(gate), c_int(T), c_int(gate.stride(0)), c_int(num_heads), c_int(vdim),
-                                       c_int(dtype_code(o.dtype)), _stream()), "head_gate")
+                                       c_int(1 if per_element else 0), c_int(dtype_code(o.dtype)), _stream()), "head_gate")
     return out
 
 
@@ -784,10 +786,11 @@ def _moe_lib():
 
 def route_topk(ids: torch.Tensor, weights: torch.Tensor, x: torch.Tensor, router: torch.Tensor,
                bias: Optional[torch.Tensor], over_all: bool = False, scale: float = 1.0,
-               extra_out: Optional[torch.Tensor] = None) -> None:
+               extra_out: Optional[torch.Tensor] = None, logistic: bool = False) -> None:
     """ids, weights [T, top]: the `top` largest of x @ router^T + bias (float32 arithmetic) and the softmax over them; with
     `over_all` the weights are `scale` times the winners' shares of the softmax over ALL experts instead.  `extra_out`
-    float32 [T, n]: the last n rows of `router` are not experts, their products with x leave there unchanged."""
+    float32 [T, n]: the last n rows of `router` are not experts, their products with x leave there unchanged.  `logistic`: the
+    weights are `scale` times the winners' own sigmoid(z), with no sum over experts."""
     _cuda(ids, weights, x, router, bias, extra_out); _contig(ids, weights, x, router, bias, extra_out)
     T, D = x.shape
     extra = 0 if extra_out is None else extra_out.shape[1]
@@ -799,13 +802,14 @@ def route_topk(ids: torch.Tensor, weights: torch.Tensor, x: torch.Tensor, router
             or ids.shape != (T, top) or weights.shape != (T, top) or (bias is not None and (bias.dtype != torch.float32 or bias.numel() != E))):
         raise KernelError("route_topk: ids int32 and weights float32 [T, top]; router float32 [E, D]; bias float32 [E]")
     _check(_moe_lib().cvb_route_topk(_ptr(ids), _ptr(weights), _ptr(x), _ptr(router), _ptr(bias), c_int(T), c_int(D), c_int(E),
-                                     c_int(top), c_int(1 if over_all else 0), c_float(scale), c_int(extra), _ptr(extra_out),
+                                     c_int(top), c_int(2 if logistic else (1 if over_all else 0)), c_float(scale), c_int(extra), _ptr(extra_out),
                                      c_int(dtype_code(x.dtype)), _stream()), "route_topk")
 
 
 def expert_rows(y: torch.Tensor, hid: torch.Tensor, x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor,
-                w_gate_up: torch.Tensor, w_down: torch.Tensor, gated: bool = True) -> torch.Tensor:
+                w_gate_up: torch.Tensor, w_down: torch.Tensor, gated: bool = True, weight_on_input: bool = False) -> torch.Tensor:
     """y[t] = sum_k weights[t, k] * down_e(silu(gate_e x) * up_e x), e = ids[t, k]; w_gate_up [E, 2 ff, D], w_down [E, D, ff];
+    with `weight_on_input` y[t] = sum_k expert_e(weights[t, k] * x) instead;
     `hid` [T * top, ff] is scratch.  Two kernels that read only the chosen experts' weights: for a few tokens, and for
     float32.  `gated=False`: an expert is down_e(relu(up_e x)^2) and w_gate_up holds [E, ff, D]."""
     _cuda(y, hid, x, ids, weights, w_gate_up, w_down); _contig(y, hid, x, ids, weights, w_gate_up, w_down)
@@ -819,8 +823,8 @@ def expert_rows(y: torch.Tensor, hid: torch.Tensor, x: torch.Tensor, ids: torch.
         raise KernelError("expert_rows: x, y [T, D], hid [T * top, ff], w_gate_up [E, 2 ff, D] and w_down [E, D, ff] of one element "
                           "type; ids int32 and weights float32 [T, top]")
     _check(_moe_lib().cvb_expert_rows(_ptr(y), _ptr(hid), _ptr(x), _ptr(ids), _ptr(weights), _ptr(w_gate_up), _ptr(w_down), c_int(T),
-                                      c_int(D), c_int(F), c_int(E), c_int(top), c_int(1 if gated else 0), c_int(dtype_code(x.dtype)),
-                                      _ptr(error_flag(x.device)), _stream()), "expert_rows", kernels=2)
+                                      c_int(D), c_int(F), c_int(E), c_int(top), c_int(1 if gated else 0), c_int(1 if weight_on_input else 0),
+                                      c_int(dtype_code(x.dtype)), _ptr(error_flag(x.device)), _stream()), "expert_rows", kernels=2)
     return y
 
 
@@ -835,7 +839,7 @@ def grouped_rows_tcgen05(num_tokens: int, top: int, num_experts: int) -> int:
 
 
 def experts_grouped_tcgen05(y, x, ids, weights, w_gate_up, w_down, tile_expert, row_token, slot_of, xs, hid, rows,
-                            gated: bool = True) -> torch.Tensor:
+                            gated: bool = True, weight_on_input: bool = False) -> torch.Tensor:
     """More tokens on the tcgen05 tensor cores: the pairs are sorted by expert into segments that start on multiples of
     128 rows (device side), the tokens' rows are gathered into that order, and two grouped products (the first with the
     gated activation as its epilogue) run on csrc/gemm_tcgen05.cu's kernel; the last kernel adds a token's expert outputs
@@ -863,7 +867,12 @@ def experts_grouped_tcgen05(y, x, ids, weights, w_gate_up, w_down, tile_expert, 
     _check(_moe_lib().cvb_sort_pairs_padded(_ptr(tile_expert), _ptr(row_token), _ptr(slot_of), _ptr(ids), c_int(T), c_int(E), c_int(top),
                                             c_int(R // 128), err, _stream()), "sort_pairs_padded")
     xs2, hid2, rows2 = xs.view(-1)[:R * D].view(R, D), hid.view(-1)[:R * F].view(R, F), rows.view(-1)[:R * D].view(R, D)
-    gather_rows(xs2, x, row_token.view(-1)[:R])
+    if weight_on_input:     # a pair's weight scales its row on the way in; the rows behind a segment keep what they held (finite)
+        _moe_lib().cvb_scatter_pairs_scaled_bf16.restype = c_int
+        _check(_moe_lib().cvb_scatter_pairs_scaled_bf16(_ptr(xs2), _ptr(x), _ptr(slot_of), _ptr(weights), c_int(T), c_int(D), c_int(top),
+                                                        _stream()), "scatter_pairs_scaled")
+    else:
+        gather_rows(xs2, x, row_token.view(-1)[:R])
     if gated:
         _check(_gemm.cvb_gemm_grouped_bf16_tcgen05(_ptr(hid2), _ptr(xs2), _ptr(w_gate_up), _ptr(tile_expert), c_int(R), c_int(2 * F), c_int(E),
                                                    c_int(D), c_int(1), c_int(256), err, _stream()), "gemm_grouped_bf16_tcgen05")
@@ -876,7 +885,8 @@ def experts_grouped_tcgen05(y, x, ids, weights, w_gate_up, w_down, tile_expert, 
     _check(_gemm.cvb_gemm_grouped_bf16_tcgen05(_ptr(rows2), _ptr(hid2), _ptr(w_down), _ptr(tile_expert), c_int(R), c_int(D), c_int(E),
                                                c_int(F), c_int(0), c_int(256 if tiles_256 >= 120 else 128), err, _stream()),
            "gemm_grouped_bf16_tcgen05")
-    _check(_moe_lib().cvb_combine_pairs_bf16(_ptr(y), _ptr(rows2), _ptr(slot_of), _ptr(weights), c_int(T), c_int(D), c_int(top), _stream()),
+    _check(_moe_lib().cvb_combine_pairs_bf16(_ptr(y), _ptr(rows2), _ptr(slot_of), _ptr(None if weight_on_input else weights), c_int(T),
+                                             c_int(D), c_int(top), _stream()),
            "combine_pairs")
     return y
 
@@ -891,7 +901,8 @@ def grouped_experts_preferred(num_pairs: int, num_experts: int, expert_bytes: in
             or (num_pairs >= 3 and expert_bytes >= (64 << 20)))
 
 
-def routed_experts(y, x, ids, weights, w_gate_up, w_down, workspace=None, kernel: str = "", gated: bool = True) -> torch.Tensor:
+def routed_experts(y, x, ids, weights, w_gate_up, w_down, workspace=None, kernel: str = "", gated: bool = True,
+                   weight_on_input: bool = False) -> torch.Tensor:
     """The experts' outputs added up with the router's weights, by the kernels that suit the step: one or two tokens (and
     float32, and sizes that are no multiples of 8) read the chosen experts' weights pair by pair; more go through the
     grouped tcgen05 products (see grouped_experts_preferred).  `workspace` (parts.base.Workspace) lends the scratch;
@@ -907,17 +918,177 @@ def routed_experts(y, x, ids, weights, w_gate_up, w_down, workspace=None, kernel
         def buf(name, n, dtype):
             if workspace is not None:
                 # sized once for the largest step (the address must not move: captured graphs hold it)
-                return workspace.flat(f"{name}_{E}_{top}", grouped_rows_tcgen05(workspace.max_tokens, top, E) * (n // R), dtype)
-            return torch.empty(n, dtype=dtype, device=x.device)
+                return workspace.flat(f"{name}_{E}_{top}", grouped_rows_tcgen05(workspace.max_tokens, top, E) * (n // R), dtype, zero=True)
+            return torch.zeros(n, dtype=dtype, device=x.device)
         slot_of = workspace.rows("moe_slot_of", T, top, torch.int32) if workspace is not None else torch.empty(T * top, dtype=torch.int32, device=x.device)
         return experts_grouped_tcgen05(y, x, ids, weights, w_gate_up, w_down, buf("moe_tile_expert", R, torch.int32),
                                        buf("moe_row_token", R, torch.int32), slot_of, buf(f"moe_xs{D}", R * D, x.dtype),
-                                       buf(f"moe_hid{F}", R * F, x.dtype), buf(f"moe_rows{D}", R * D, x.dtype), gated=gated)
+                                       buf(f"moe_hid{F}", R * F, x.dtype), buf(f"moe_rows{D}", R * D, x.dtype), gated=gated,
+                                       weight_on_input=weight_on_input)
     if workspace is not None:
         hid = workspace.rows("moe_hidden", T, top * F, x.dtype)
     else:
         hid = torch.empty((T, top * F), dtype=x.dtype, device=x.device)
-    return expert_rows(y, hid, x, ids, weights, w_gate_up, w_down, gated=gated)
+    return expert_rows(y, hid, x, ids, weights, w_gate_up, w_down, gated=gated, weight_on_input=weight_on_input)
+
+
+# ---- several residual streams read and written through learned weights (csrc/hyper.cu) ------------------------------------
+
+_hyper = None
+
+
+def _hyper_lib():
+    global _hyper
+    if _hyper is None:
+        lib = load_library("hyper")
+        for name in ("cvb_stream_embed", "cvb_stream_step"):
+            getattr(lib, name).restype = c_int
+        _hyper = lib
+    return _hyper
+
+
+def stream_embed(X: torch.Tensor, table: torch.Tensor, tokens: torch.Tensor, streams: int) -> torch.Tensor:
+    """X (float32 [T, streams * D]): every stream of a token starts as its row of `table` [vocab, D]."""
+    _cuda(X, table, tokens); _contig(X, table, tokens)
+    T = X.shape[0]
+    V, D = table.shape
+    if X.dtype != torch.float32 or X.shape[1] != streams * D or tokens.dtype != torch.int32 or tokens.numel() < T:
+        raise KernelError("stream_embed: X float32 [T, streams * D], tokens int32 [T]")
+    _check(_hyper_lib().cvb_stream_embed(_ptr(X), _ptr(table), _ptr(tokens), c_int(T), c_int(streams), c_int(D), c_int(V),
+                                         c_int(dtype_code(table.dtype)), _ptr(error_flag(X.device)), _stream()), "stream_embed")
+    return X
+
+
+def stream_step(X: torch.Tensor, streams: int, write=None, read=None, eps: float = 0.0, out: Optional[torch.Tensor] = None):
+    """One pass over the streams X (float32 [T, streams * D], in place).  `write` = (y [T, D], mix float32 [S, S] (from, to),
+    b float32 [S]): x_t <- sum_s mix[s, t] x_s + b_t y.  `read` = (a float32 [S] or None for ones, g float32 with one element
+    or None for 1) with `out` [T, D]: out = T(u / sqrt(mean(u^2) + eps) * g), u = sum_s a_s x_s, of the streams after the write."""
+    T = X.shape[0]
+    S = int(streams)
+    D = X.shape[1] // S
+    y = mix = b = a = g = None
+    if write is not None:
+        y, mix, b = write
+    if read is not None:
+        a, g = read
+        if out is None:
+            raise KernelError("stream_step: a read needs an output")
+    _cuda(X, y, mix, b, a, g, out); _contig(X, y, mix, b, a, g, out)
+    act = out.dtype if out is not None else y.dtype
+    if X.dtype != torch.float32 or X.shape[1] != S * D:
+        raise KernelError("stream_step: the streams are float32 [T, S * D]")
+    if y is not None and (y.shape != (T, D) or y.dtype != act or mix.dtype != torch.float32 or mix.numel() != S * S
+                          or b.dtype != torch.float32 or b.numel() != S):
+        raise KernelError("stream_step: write = (y [T, D], mix float32 [S, S], b float32 [S])")
+    if out is not None and (out.shape != (T, D) or (a is not None and (a.dtype != torch.float32 or a.numel() != S))
+                            or (g is not None and (g.dtype != torch.float32 or g.numel() != 1))):
+        raise KernelError("stream_step: read = (a float32 [S], g float32 [1]) into out [T, D]")
+    _check(_hyper_lib().cvb_stream_step(_ptr(X), _ptr(y), _ptr(mix), _ptr(b), _ptr(a), _ptr(g), c_float(eps), _ptr(out), c_int(T),
+                                        c_int(S), c_int(D), c_int(dtype_code(act)), _stream()), "stream_step")
+    return out if out is not None else X
+
+
+# ---- attention over entries of a key and its value with chunk, window, pooled blocks, cap, distance term and sink ----------
+
+_attn_masked = None
+
+
+def _attn_masked_lib():
+    global _attn_masked
+    if _attn_masked is None:
+        lib = load_library("attn_masked")
+        for name in ("cvb_masked_qkv_prep", "cvb_pool_entries", "cvb_attn_masked_general"):
+            getattr(lib, name).restype = c_int
+        _attn_masked = lib
+    return _attn_masked
+
+
+def masked_qkv_prep(q_out: torch.Tensor, packed: torch.Tensor, num_heads: int, num_kv_heads: int, dim: int, vdim: int, eps: float,
+                    q_weight: Optional[torch.Tensor] = None, k_weight: Optional[torch.Tensor] = None,
+                    cos: Optional[torch.Tensor] = None, sin: Optional[torch.Tensor] = None, rot: int = 0, interleaved: bool = True,
+                    positions: Optional[torch.Tensor] = None, pages: Optional[torch.Tensor] = None,
+                    slots: Optional[torch.Tensor] = None, page_size: int = 1, planes: int = 1,
+                    v_first_out: Optional[torch.Tensor] = None, v_first_in: Optional[torch.Tensor] = None,
+                    lam: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """From rows [q: H dim | k: G dim | v: G vdim] of `packed`: q_out [T, H, dim] = turn(norm(q)); the entry [turn(norm(k)) | v']
+    of every kv head into the token's cache slot of `pages` ([page, planes, G, slot, dim + vdim], plane 0), with
+    v' = (1 - lam) v + lam v_first_in (v itself without v_first_in); `v_first_out` [T, G * vdim] receives v as projected."""
+    _cuda(q_out, packed, q_weight, k_weight, cos, sin, positions, pages, slots, v_first_out, v_first_in, lam)
+    _contig(q_out, packed, q_weight, k_weight, cos, sin, positions, pages, slots, v_first_out, v_first_in, lam)
+    T = packed.shape[0]
+    H, G = num_heads, num_kv_heads
+    if q_out.dtype != packed.dtype or q_out.numel() != T * H * dim or packed.shape[1] < H * dim + G * (dim + vdim):
+        raise KernelError("masked_qkv_prep: packed [T, H dim + G (dim + vdim)] and q_out [T, H, dim] of one element type")
+    for w in (q_weight, k_weight):
+        if w is not None and (w.dtype != torch.float32 or w.numel() != dim):
+            raise KernelError("masked_qkv_prep: norm weights are float32 [dim]")
+    max_pos = 0
+    if rot:
+        if cos is None or sin is None or cos.dtype != torch.float32 or sin.shape != cos.shape or cos.shape[1] != rot // 2 or positions is None:
+            raise KernelError("masked_qkv_prep: a rotation needs float32 tables [positions, rot / 2] and the positions")
+        max_pos = cos.shape[0]
+    for t in (pages, v_first_out, v_first_in):
+        if t is not None and t.dtype != packed.dtype:
+            raise KernelError("masked_qkv_prep: pages and kept values share the rows' element type")
+    for t in (v_first_out, v_first_in):
+        if t is not None and t.numel() < T * G * vdim:
+            raise KernelError("masked_qkv_prep: kept values are [T, G * vdim]")
+    if v_first_in is not None and (lam is None or lam.dtype != torch.float32 or lam.numel() != 1):
+        raise KernelError("masked_qkv_prep: mixing needs a float32 weight of one element")
+    for t in (positions, slots):
+        if t is not None and (t.dtype != torch.int32 or t.numel() < T):
+            raise KernelError("masked_qkv_prep: positions and slots are int32 [T]")
+    total_slots = pages.numel() // (planes * G * (dim + vdim)) if pages is not None else 0
+    _check(_attn_masked_lib().cvb_masked_qkv_prep(
+        _ptr(q_out), _ptr(packed), c_int(T), c_int(packed.shape[1]), _ptr(q_weight), _ptr(k_weight), _ptr(cos if rot else None),
+        _ptr(sin if rot else None), _ptr(positions), _ptr(slots), _ptr(pages), _ptr(v_first_out), _ptr(v_first_in), _ptr(lam),
+        c_int(H), c_int(G), c_int(dim), c_int(vdim), c_int(rot), c_int(1 if interleaved else 0), c_int(planes), c_int(page_size),
+        c_int(max_pos), c_float(eps), c_int64(total_slots), c_int(dtype_code(packed.dtype)), _ptr(error_flag(packed.device)),
+        _stream()), "masked_qkv_prep")
+    return q_out
+
+
+def pool_entries(pages: torch.Tensor, block_tables: torch.Tensor, seq_of_token: torch.Tensor, positions: torch.Tensor,
+                 num_tokens: int, num_kv_heads: int, entry_width: int, pool: int, page_size: int) -> None:
+    """Tokens of the step whose position closes a block of `pool` positions write the mean of the block's entries (plane 0 of
+    `pages` [page, 2, G, slot, entry_width]) into plane 1 at the place of position (p + 1) / pool - 1."""
+    _cuda(pages, block_tables, seq_of_token, positions); _contig(pages, block_tables, seq_of_token, positions)
+    if block_tables.dtype != torch.int32 or seq_of_token.dtype != torch.int32 or positions.dtype != torch.int32:
+        raise KernelError("pool_entries: index tensors are int32")
+    num_pages = pages.numel() // (2 * num_kv_heads * page_size * entry_width)
+    _check(_attn_masked_lib().cvb_pool_entries(_ptr(pages), _ptr(block_tables), c_int(block_tables.shape[1]), _ptr(seq_of_token),
+                                               _ptr(positions), c_int(num_tokens), c_int(num_kv_heads), c_int(entry_width), c_int(pool),
+                                               c_int(page_size), c_int(num_pages), c_int(dtype_code(pages.dtype)),
+                                               _ptr(error_flag(pages.device)), _stream()), "pool_entries")
+
+
+def attn_masked_general(out: torch.Tensor, q: torch.Tensor, pages: torch.Tensor, block_tables: torch.Tensor,
+                        seq_of_token: torch.Tensor, positions: torch.Tensor, num_tokens: int, num_heads: int, num_kv_heads: int,
+                        dim: int, vdim: int, page_size: int, scale: float, planes: int = 1, chunk: int = 0, window: int = 0,
+                        pool: int = 0, softcap: float = 0.0, r1: Optional[torch.Tensor] = None, r2: Optional[torch.Tensor] = None,
+                        sink: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out [T, H, vdim]: one block per (token, query head), any sizes, float32 or bf16 (see csrc/attention_masked.cu).
+    `gate` [T, H] (a view with unit column stride): the head's output is multiplied by sigmoid(gate[t, h])."""
+    _cuda(out, q, pages, block_tables, seq_of_token, positions, r1, r2, sink, gate)
+    _contig(out, q, pages, block_tables, seq_of_token, positions, r1, r2, sink)
+    T, H, G = num_tokens, num_heads, num_kv_heads
+    if q.dtype != pages.dtype or out.dtype != q.dtype or q.numel() < T * H * dim or out.numel() < T * H * vdim:
+        raise KernelError("attn_masked: q [T, H, dim], out [T, H, vdim] and the pages share one element type")
+    if block_tables.dtype != torch.int32 or block_tables.dim() != 2 or seq_of_token.dtype != torch.int32 or positions.dtype != torch.int32:
+        raise KernelError("attn_masked: block_tables int32 [S, W]; seq_of_token and positions int32")
+    for t in (r1, r2, sink):
+        if t is not None and (t.dtype != torch.float32 or t.numel() != H):
+            raise KernelError("attn_masked: r1, r2 and sink are float32 [H]")
+    if gate is not None and (gate.dtype != q.dtype or gate.shape[1] != H or gate.stride(1) != 1 or gate.shape[0] < T):
+        raise KernelError("attn_masked: gate [T, H] of the queries' element type")
+    num_pages = pages.numel() // (planes * G * page_size * (dim + vdim))
+    _check(_attn_masked_lib().cvb_attn_masked_general(
+        _ptr(out), _ptr(q), _ptr(pages), _ptr(block_tables), c_int(block_tables.shape[1]), _ptr(seq_of_token), _ptr(positions),
+        c_int(T), c_int(H), c_int(G), c_int(dim), c_int(vdim), c_int(page_size), c_int(planes), c_int(chunk), c_int(window),
+        c_int(pool), c_float(scale), c_float(softcap), _ptr(r1), _ptr(r2), _ptr(sink), _ptr(gate),
+        c_int(gate.stride(0) if gate is not None else 0), c_int(num_pages), c_int(dtype_code(q.dtype)),
+        _ptr(error_flag(q.device)), _stream()), "attn_masked_general")
+    return out
 
 
 # ---- projection epilogue: per-head norm, rotary, cache write --------------------------------------------------

@@ -1,2 +1,2 @@
 """Architectures.  Importing this package registers them."""
-from . import dugulorn, givirax, lorulix, qwen3  # noqa: F401
+from . import dugulorn, givirax, lorulix, qwen3, rumurax  # noqa: F401

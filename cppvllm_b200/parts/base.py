@@ -66,7 +66,7 @@ class WeightSpec:
     role: str = "matrix"      # "matrix": operand of a matrix product / embedding table (engine dtype, or float32
                               #           if stored so); "vector": norm weights and the like (always float32);
                               # "int_table": integer look-up table (int32)
-    init: str = "normal"      # random weights: "normal" = N(0, std), "norm" = 1 + U(-spread, spread)
+    init: str = "normal"      # random weights: "normal" = N(0, std), "norm" = 1 + U(-spread, spread), "eye" = identity + U(-spread, spread)
 
 
 @dataclass(frozen=True)

@@ -14,6 +14,8 @@ whose first kv_rank elements are also the value: one kv head and a value narrowe
 (csrc/attention_keys.cu) for bf16 entries of up to 128 elements in steps of 16, else in csrc/attention_general.cu.  The two per-head products are batched library products.  The rotation turns the first ``rot`` elements of the
 positional parts in pairs (2i, 2i+1); the rest pass.  ``reads_other_cache``: the layer has no dkv projection and reads the
 entries another layer wrote (the run list names the unit), with its own up-projections, queries and gate.
+``q_rank = 0``: the queries have no latent of their own, q = Wq x (tensor ``q``).  ``gate = "element"``: the gate has one number
+per element of the concatenated heads (Wg is [H * value_dim, D]): y = Wo (concat_h(o_h) * sigmoid(Wg x)).
 """
 from __future__ import annotations
 
@@ -28,8 +30,8 @@ from .base import CacheSpec, Mixer, WeightSpec, register_part
 @register_part("mixer", "latent_attention")
 class LatentAttention(Mixer):
     def __init__(self, runtime, prefix="", names=None, *, hidden_size: int, num_heads: int, nope_dim: int, rot_dim: int,
-                 value_dim: int, q_rank: int, kv_rank: int, scale: float, eps: float, position, rot: int = -1,
-                 reads_other_cache: bool = False):
+                 value_dim: int, q_rank: int = 0, kv_rank: int, scale: float, eps: float, position, rot: int = -1,
+                 reads_other_cache: bool = False, gate: str = "head"):
         super().__init__(runtime, prefix, names)
         self.hidden_size, self.num_heads, self.nope_dim, self.rot_dim = int(hidden_size), int(num_heads), int(nope_dim), int(rot_dim)
         self.value_dim, self.q_rank, self.kv_rank = int(value_dim), int(q_rank), int(kv_rank)
@@ -39,6 +41,9 @@ class LatentAttention(Mixer):
         if self.rot > self.rot_dim or self.rot != position.rotary_dim or not position.interleaved:
             raise ValueError("the positional part is turned in pairs (2i, 2i+1) over at most its own width")
         self.own_cache = not reads_other_cache
+        if gate not in ("head", "element"):
+            raise ValueError(f"gate is 'head' or 'element', got {gate!r}")
+        self.gate_cols = self.num_heads if gate == "head" else self.num_heads * self.value_dim
         self.w_down = self.w_uq = self.w_uk = self.w_uv = self.w_o = self.w_qnorm = self.w_kvnorm = None
 
     def cache_spec(self) -> CacheSpec:
@@ -47,14 +52,17 @@ class LatentAttention(Mixer):
     def weight_specs(self) -> Dict[str, WeightSpec]:
         D, H = self.hidden_size, self.num_heads
         specs = {
-            self.full_name("dq"): WeightSpec((self.q_rank, D)),
-            self.full_name("dq.norm"): WeightSpec((self.q_rank,), role="vector", init="norm"),
-            self.full_name("uq"): WeightSpec((H * (self.nope_dim + self.rot_dim), self.q_rank)),
             self.full_name("uk"): WeightSpec((H * self.nope_dim, self.kv_rank)),
             self.full_name("uv"): WeightSpec((H * self.value_dim, self.kv_rank)),
-            self.full_name("g"): WeightSpec((H, D)),
+            self.full_name("g"): WeightSpec((self.gate_cols, D)),
             self.full_name("o"): WeightSpec((D, H * self.value_dim)),
         }
+        if self.q_rank:
+            specs[self.full_name("dq")] = WeightSpec((self.q_rank, D))
+            specs[self.full_name("dq.norm")] = WeightSpec((self.q_rank,), role="vector", init="norm")
+            specs[self.full_name("uq")] = WeightSpec((H * (self.nope_dim + self.rot_dim), self.q_rank))
+        else:
+            specs[self.full_name("q")] = WeightSpec((H * (self.nope_dim + self.rot_dim), D))
         if self.own_cache:
             specs[self.full_name("dkv")] = WeightSpec((self.kv_rank + self.rot_dim, D))
             specs[self.full_name("dkv.norm")] = WeightSpec((self.kv_rank,), role="vector", init="norm")
@@ -62,15 +70,15 @@ class LatentAttention(Mixer):
 
     def bind(self, tensors) -> None:
         t = lambda n: tensors[self.full_name(n)]          # noqa: E731
-        rows = [t("dq")] + ([t("dkv")] if self.own_cache else []) + [t("g")]
+        rows = ([t("dq")] if self.q_rank else []) + ([t("dkv")] if self.own_cache else []) + [t("g")]
         if len({r.dtype for r in rows}) > 1:
             rows = [r.float() for r in rows]
         self.w_down = torch.cat(rows, dim=0).contiguous()
         self.kv_off = self.q_rank
         self.g_off = self.q_rank + (self.kv_rank + self.rot_dim if self.own_cache else 0)
-        self.w_qnorm = t("dq.norm")
+        self.w_qnorm = t("dq.norm") if self.q_rank else None
         self.w_kvnorm = t("dkv.norm") if self.own_cache else None
-        self.w_uq, self.w_o = t("uq"), t("o")
+        self.w_uq, self.w_o = (t("uq") if self.q_rank else t("q")), t("o")
         H = self.num_heads
         self.w_uk = t("uk").view(H, self.nope_dim, self.kv_rank)                        # q_abs_h = q_nope_h @ Wuk_h
         self.w_uv = t("uv").view(H, self.value_dim, self.kv_rank).transpose(1, 2)       # o_h = o_lat_h @ Wuv_h^T
@@ -88,11 +96,11 @@ class LatentAttention(Mixer):
         g = ctx.groups[cache.group]
         pos = self.position
         packed = self._project(x, self.w_down, ws.rows("lat_down", T, self.w_down.shape[0], x.dtype), T)
-        cq = ws.rows("lat_cq", T, self.q_rank, x.dtype)
+        cq = ws.rows("lat_cq", T, self.q_rank, x.dtype) if self.q_rank else None
         writes = self.own_cache and cache.writes
         ops.latent_prep(packed, cq, 0, self.q_rank, self.w_qnorm, cache.pages if writes else None, self.kv_off, R, dr, self.rot,
                         self.w_kvnorm, pos.cos, pos.sin, ctx.positions, g.slot_mapping if writes else None, self.eps)
-        q = self._project(cq, self.w_uq, ws.rows("lat_q", T, H * (dn + dr), x.dtype), T)
+        q = self._project(cq if self.q_rank else x, self.w_uq, ws.rows("lat_q", T, H * (dn + dr), x.dtype), T)
         q_abs = ws.rows("lat_qabs", T, H * R, x.dtype).view(H, T, R)
         torch.bmm(q.view(T, H, dn + dr)[:, :, :dn].transpose(0, 1), self.w_uk, out=q_abs)
         q_att = ops.latent_q_assemble(ws.rows("lat_qatt", T, H * (R + dr), x.dtype), q_abs, q, H, dn, R, dr, self.rot, pos.cos,
@@ -101,7 +109,8 @@ class LatentAttention(Mixer):
         self.attend(o_lat, q_att, ctx, cache, g)
         o_heads = ws.rows("lat_ov", T, H * dv, x.dtype).view(H, T, dv)
         torch.bmm(o_lat.view(T, H, R).transpose(0, 1), self.w_uv, out=o_heads)
-        att = ops.head_gate(ws.rows("attn_out", T, H * dv, x.dtype), o_heads, packed[:, self.g_off:self.g_off + H], H, dv)
+        att = ops.head_gate(ws.rows("attn_out", T, H * dv, x.dtype), o_heads, packed[:, self.g_off:self.g_off + self.gate_cols], H, dv,
+                            per_element=self.gate_cols != H)
         return self._project(att, self.w_o, ws.rows("attn_proj", T, self.hidden_size, x.dtype), T)
 
     def attend(self, o_lat, q_att, ctx, cache, g):

@@ -150,7 +150,7 @@ class CausalLM:
         if getattr(pending, "weight", None) is not None and pending.weight is getattr(self.final_norm, "weight", None):
             # the last block has applied the final norm already: only the wanted rows are picked
             return self.head.forward(ops.gather_rows(normed, pending.rows, ctx.logit_rows), logits_out[:R])
-        rows_h = ops.gather_rows(ws.rows("head_rows", R, self.hidden_size, h.dtype), h, ctx.logit_rows)
+        rows_h = ops.gather_rows(ws.rows("head_rows", R, h.shape[1], h.dtype), h, ctx.logit_rows)     # several streams: a wider row
         if isinstance(pending, tuple):               # several deltas (a block whose sublayers run side by side)
             rows_p = tuple(ops.gather_rows(ws.rows(f"head_pending{i}", R, self.hidden_size, p.dtype), p, ctx.logit_rows)
                            for i, p in enumerate(pending))

@@ -9,7 +9,10 @@
   [E, D, ff], so that a kernel reaches every expert from one base address.  One or two tokens read only their chosen
   experts' weights pair by pair (two kernels spread over all SMs); more are sorted by expert on the device and go through
   two grouped products on the tcgen05 kernel (csrc/moe.cu, csrc/gemm_tcgen05.cu); nothing travels to the host, so steps
-  stay capturable.
+  stay capturable.  Options: ``score = "sigmoid"``: the chosen experts' weights are their own sigmoid(z_e), not renormalised;
+  ``weight_on_input``: the weight multiplies the expert's input, y = sum_e expert_e(w_e x); ``router_bias = False``: no bias
+  tensor; ``shared_size`` > 0: a shared expert of the same gated form (``<prefix>shared.gate|up|down``) runs for every token
+  and is added.
 * ``clamped_glu``: dense and gated with clamps: g = min(Wgate x, L), u = clamp(Wup x, -L, L); y = Wdown (g sigmoid(alpha g) (u + 1)).
 * ``routed_act``: a mixture of ungated experts Wdown act(Wup x) (act = relu2) whose weights are `scale` times the chosen experts'
   shares of the softmax over ALL experts (not renormalised over the winners); no router bias.  Optionally a shared expert of
@@ -77,50 +80,78 @@ class ActMLP(FeedForward):
 @register_part("ffn", "routed_glu")
 class RoutedGLU(FeedForward):
     def __init__(self, runtime, prefix="", names=None, *, hidden_size: int, intermediate_size: int, num_experts: int, top: int,
-                 router_name: str = "router", router_bias_name: str = "router.b", expert_prefix: str = "e"):
+                 router_name: str = "router", router_bias_name: str = "router.b", expert_prefix: str = "e", score: str = "softmax",
+                 weight_on_input: bool = False, router_bias: bool = True, shared_size: int = 0, shared_prefix: str = "shared."):
         super().__init__(runtime, prefix, names)
         self.hidden_size, self.intermediate_size = int(hidden_size), int(intermediate_size)
         self.num_experts, self.top = int(num_experts), int(top)
         if not (0 < self.top <= self.num_experts):
             raise ValueError(f"a token cannot use {self.top} of {self.num_experts} experts")
+        if score not in ("softmax", "sigmoid"):
+            raise ValueError(f"score is 'softmax' (over the chosen experts) or 'sigmoid', got {score!r}")
         self.router_name, self.router_bias_name, self.expert_prefix = router_name, router_bias_name, expert_prefix
-        self.w_router = self.b_router = self.w_gate_up = self.w_down = None
+        self.score, self.weight_on_input, self.router_bias = score, bool(weight_on_input), bool(router_bias)
+        self.shared_size, self.shared_prefix = int(shared_size), shared_prefix
+        self.w_router = self.b_router = self.w_gate_up = self.w_down = self.shared_gate_up = self.shared_down = None
 
     def _expert(self, e: int, which: str) -> str:
         return self.full_name(f"{self.expert_prefix}{e}.{which}")
 
     def weight_specs(self) -> Dict[str, WeightSpec]:
         D, I, E = self.hidden_size, self.intermediate_size, self.num_experts
-        specs = {self.full_name(self.router_name): WeightSpec((E, D), role="vector"),
-                 self.full_name(self.router_bias_name): WeightSpec((E,), role="vector")}
+        specs = {self.full_name(self.router_name): WeightSpec((E, D), role="vector")}
+        if self.router_bias:
+            specs[self.full_name(self.router_bias_name)] = WeightSpec((E,), role="vector")
         for e in range(E):
             specs[self._expert(e, "gate")] = WeightSpec((I, D))
             specs[self._expert(e, "up")] = WeightSpec((I, D))
             specs[self._expert(e, "down")] = WeightSpec((D, I))
+        if self.shared_size:
+            sp = self.shared_prefix
+            specs[self.full_name(sp + "gate")] = WeightSpec((self.shared_size, D))
+            specs[self.full_name(sp + "up")] = WeightSpec((self.shared_size, D))
+            specs[self.full_name(sp + "down")] = WeightSpec((D, self.shared_size))
         return specs
 
     def bind(self, tensors) -> None:
         E = self.num_experts
         self.w_router = tensors[self.full_name(self.router_name)]
-        self.b_router = tensors[self.full_name(self.router_bias_name)]
+        self.b_router = tensors[self.full_name(self.router_bias_name)] if self.router_bias else None
+        if self.shared_size:
+            sp = self.shared_prefix
+            g, u = tensors[self.full_name(sp + "gate")], tensors[self.full_name(sp + "up")]
+            if g.dtype != u.dtype:
+                g, u = g.float(), u.float()
+            self.shared_gate_up = torch.cat([g, u], dim=0).contiguous()
+            self.shared_down = tensors[self.full_name(sp + "down")]
         gu = [torch.cat([tensors[self._expert(e, "gate")], tensors[self._expert(e, "up")]], dim=0) for e in range(E)]
         self.w_gate_up = torch.stack(gu, dim=0).to(self.rt.dtype).contiguous()
         self.w_down = torch.stack([tensors[self._expert(e, "down")] for e in range(E)], dim=0).to(self.rt.dtype).contiguous()
 
     def weight_bytes(self) -> int:
-        """What a decoded token reads: the router and `top` of the experts."""
+        """What a decoded token reads: the router, `top` of the experts and the shared expert."""
         per_expert = (self.w_gate_up.numel() + self.w_down.numel()) * self.w_down.element_size() // self.num_experts
-        return self.w_router.numel() * 4 + self.b_router.numel() * 4 + self.top * per_expert
+        shared = sum(w.numel() * w.element_size() for w in (self.shared_gate_up, self.shared_down)) if self.shared_size else 0
+        return self.w_router.numel() * 4 + (self.b_router.numel() * 4 if self.router_bias else 0) + self.top * per_expert + shared
+
+    def _project(self, x, w, out, rows):
+        return ops.linear(x, w, out=out) if self.rt.plain_kernels else ops.project_rows(x, w, out, rows)
 
     def forward(self, x, ctx):
         T = x.shape[0]
         ws = self.rt.workspace
         ids = ws.rows("moe_ids", T, self.top, torch.int32)
         weights = ws.rows("moe_weights", T, self.top, torch.float32)
-        ops.route_topk(ids, weights, x, self.w_router, self.b_router)
+        ops.route_topk(ids, weights, x, self.w_router, self.b_router, logistic=self.score == "sigmoid")
         y = ws.rows("ffn_out", T, self.hidden_size, x.dtype)
-        return ops.routed_experts(y, x, ids, weights, self.w_gate_up, self.w_down, workspace=ws,
-                                  kernel="rows" if self.rt.plain_kernels else "")
+        ops.routed_experts(y, x, ids, weights, self.w_gate_up, self.w_down, workspace=ws,
+                           kernel="rows" if self.rt.plain_kernels else "", weight_on_input=self.weight_on_input)
+        if self.shared_size:
+            gu = self._project(x, self.shared_gate_up, ws.rows("ffn_gate_up", T, 2 * self.shared_size, x.dtype), T)
+            act = ops.swiglu(ws.rows("ffn_act", T, self.shared_size, x.dtype), gu)
+            s = self._project(act, self.shared_down, ws.rows("ffn_shared", T, self.hidden_size, x.dtype), T)
+            ops.add_(y, s)
+        return y
 
 
 @register_part("ffn", "clamped_glu")

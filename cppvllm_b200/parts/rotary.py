@@ -20,14 +20,15 @@ from .base import PositionEncoding, register_part
 
 @register_part("position", "rotary")
 class RotaryEmbedding(PositionEncoding):
-    def __init__(self, runtime, prefix="", names=None, *, rotary_dim: int, theta: float, max_positions: int,
+    def __init__(self, runtime, prefix="", names=None, *, rotary_dim: int, theta: float, max_positions: int = 0,
                  pairing: str = "half"):
         super().__init__(runtime, prefix, names)
         if rotary_dim <= 0 or rotary_dim % 2:
             raise ValueError(f"rotary_dim must be positive and even, got {rotary_dim}")
         if pairing not in ("half", "interleaved"):
             raise ValueError(f"pairing must be 'half' or 'interleaved', got {pairing!r}")
-        self.rotary_dim, self.theta, self.max_positions, self.pairing = int(rotary_dim), float(theta), int(max_positions), pairing
+        self.rotary_dim, self.theta, self.pairing = int(rotary_dim), float(theta), pairing
+        self.max_positions = int(max_positions) or int(runtime.max_positions)      # no limit named: the engine's longest sequence
         idx = torch.arange(0, self.rotary_dim, 2, dtype=torch.float64)
         inv_freq = torch.pow(torch.tensor(self.theta, dtype=torch.float64), idx / self.rotary_dim).reciprocal()
         angle = torch.outer(torch.arange(self.max_positions, dtype=torch.float64), inv_freq)

@@ -4,7 +4,7 @@ has no such mode.
 
 Every tensor the architecture declares is drawn from its own generator, seeded by (seed, tensor name): the
 values do not depend on the order of tensors.  Matrices and tables ~ N(0, std); norm weights ~ 1 + U(-spread,
-spread).  Values are drawn in float32 and stored in `store_dtype` (bfloat16 by default).
+spread); square mixing matrices ("eye") ~ identity + U(-spread, spread).  Values are drawn in float32 and stored in `store_dtype` (bfloat16 by default).
 """
 from __future__ import annotations
 
@@ -45,7 +45,9 @@ def random_tensors(config_dict: Mapping[str, Any], seed: int, std: float = 0.02,
         if ws.role == "int_table":
             out[name] = torch.randint(0, 2 ** 15, ws.shape, generator=g, dtype=torch.int32)
             continue
-        if ws.init == "norm":
+        if ws.init == "eye":              # a square matrix near the identity (weights that mix several residual streams)
+            t = torch.eye(ws.shape[0], dtype=torch.float32) + (torch.rand(ws.shape, generator=g, dtype=torch.float32) * 2.0 - 1.0) * norm_spread
+        elif ws.init == "norm":
             t = 1.0 + (torch.rand(ws.shape, generator=g, dtype=torch.float32) * 2.0 - 1.0) * norm_spread
         else:
             t = torch.randn(ws.shape, generator=g, dtype=torch.float32) * std
