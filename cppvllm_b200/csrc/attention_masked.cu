@@ -22,7 +22,17 @@
 //   attn_masked_general : one block per (token, query head), any sizes, float or bf16: the 32-bit path and the oracle of the
 //                     tensor-core forms.  Keys are walked in tiles of the block's size from the start of each run, so the
 //                     order of the float sums depends only on the token's own position.
+//   attn_masked_kernel : bf16 on the tensor cores (`mma.sync.m16n8k16`, float accumulation), key and value sizes 16..128 in
+//                     steps of 16.  A block owns 64 query rows of one kv head (64 / g tokens of one request times the g heads
+//                     of the group) and walks 64-entry tiles gathered through the block table by 16-byte cp.async into two
+//                     stages: first the pooled blocks any of its tokens sees (plane 1), then the tokens from the first one
+//                     its first token sees to its last token.  One gather feeds both products (S = Q K^T from the entry's
+//                     first dk columns, O += P V from the rest, read transposed).  Mask, cap, distance term and the base-2
+//                     online softmax work on the score fragments in registers; a sink starts a row's maximum and sum.  Tiles
+//                     are aligned to absolute positions, so a token's sums do not depend on how its prompt was cut.
 #include "common.cuh"
+#include "sm100.cuh"
+#include "mma_tiles.cuh"
 
 namespace cvb {
 
@@ -232,6 +242,271 @@ attn_masked_general_kernel(T* __restrict__ out, const T* __restrict__ q, const T
     }
 }
 
+// ---- bf16 on the tensor cores ------------------------------------------------------------------------------------------
+
+constexpr int kMTileKeys = 64;
+constexpr int kMTileRows = 64;
+constexpr int kMThreads = 128;
+constexpr float kLog2eM = 1.4426950408889634f;
+
+struct MaskedAttnParams {
+    __nv_bfloat16* out;                 // [T, H * dv]
+    const __nv_bfloat16* q;             // [T, H * dk]
+    const __nv_bfloat16* pages;         // [num_pages, planes, G, page_size, dk + dv]
+    const __nv_bfloat16* gate;          // [T, gate_stride] or null
+    const float* r1;                    // [H] or null
+    const float* r2;
+    const float* sink;                  // [H] or null
+    const int* block_tables;            // [S, table_width]
+    const int* cu_seqlens;              // [S + 1]
+    const int* positions;               // [T]
+    int gate_stride, table_width, S, H, G, dk, dv, page_size, page_shift, num_pages, planes;
+    MaskParams mp;
+    int* err;
+};
+
+__device__ __forceinline__ float tanh_by_exp(float x) { return 1.f - 2.f / (1.f + __expf(2.f * x)); }
+
+template <int W, bool EXACT>
+__global__ void __launch_bounds__(kMThreads, W <= 64 ? 3 : 2)
+attn_masked_kernel(const MaskedAttnParams p) {
+    pdl_trigger();
+    pdl_wait();
+    const int dk = EXACT ? W : p.dk, dv = EXACT ? W : p.dv;
+    const int E = dk + dv;
+    const int LDQ = dk + 8, LD = E + 8;                   // padded rows, in elements
+    const int CQ = dk >> 3, CE = E >> 3;                  // 16-byte chunks per row
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    __nv_bfloat16* sQ = reinterpret_cast<__nv_bfloat16*>(smem_raw);
+    __nv_bfloat16* sK = sQ + kMTileRows * LDQ;            // two stages of kMTileKeys * LD
+
+    const int g = p.H / p.G;
+    const int tok_per_tile = kMTileRows / g;
+    const int kvh = blockIdx.y;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+
+    int seq = -1, q0 = 0, q_len = 0, cu0 = 0;
+    {
+        int tile = blockIdx.x;
+        for (int s = 0; s < p.S; ++s) {
+            const int a = p.cu_seqlens[s], n = p.cu_seqlens[s + 1] - a;
+            const int tiles = (n + tok_per_tile - 1) / tok_per_tile;
+            if (tile < tiles) { seq = s; q0 = tile * tok_per_tile; q_len = n; cu0 = a; break; }
+            tile -= tiles;
+        }
+    }
+    if (seq < 0) return;
+    const int n_tok = min(tok_per_tile, q_len - q0);
+    const int* table = p.block_tables + static_cast<int64_t>(seq) * p.table_width;
+    const int pos_first = p.positions[cu0 + q0];
+    const int key_hi = pos_first + n_tok - 1;             // a request's tokens of a step sit at consecutive positions
+    // both bounds grow with the position: the block's first token sees the earliest token, its last one the most blocks
+    const int nb_max = visible_blocks(key_hi, p.mp);
+    const int n_pool_tiles = (nb_max + kMTileKeys - 1) / kMTileKeys;
+    const int tok_tile0 = first_visible(pos_first, p.mp) / kMTileKeys;
+    const int n_tiles = n_pool_tiles + key_hi / kMTileKeys - tok_tile0 + 1;
+
+    for (int i = threadIdx.x; i < kMTileRows * CQ; i += kMThreads) {
+        const int r = i / CQ, c = i - r * CQ;
+        const int tok = r / g;
+        const bool valid = tok < n_tok;
+        const __nv_bfloat16* src = valid ? p.q + (static_cast<int64_t>(cu0 + q0 + tok) * p.H + kvh * g + r % g) * dk + c * 8 : p.q;
+        cp_async16(sQ + r * LDQ + c * 8, src, valid);
+    }
+
+    const int ld_r0 = threadIdx.x / CE, ld_c0 = threadIdx.x - ld_r0 * CE;
+    const int ld_dr = kMThreads / CE, ld_dc = kMThreads - ld_dr * CE;
+    auto load_tile = [&](int it, int stage) {
+        const bool pooled = it < n_pool_tiles;
+        const int key0 = pooled ? it * kMTileKeys : (tok_tile0 + it - n_pool_tiles) * kMTileKeys;
+        const int hi = pooled ? nb_max - 1 : key_hi;
+        const int plane = pooled ? 1 : 0;
+        __nv_bfloat16* dst = sK + stage * kMTileKeys * LD;
+        int last_slot = -1, page = -1;                    // a thread's rows ascend: the block table is read once per page
+        int r = ld_r0, c = ld_c0;
+        for (; r < kMTileKeys; r += ld_dr, c += ld_dc) {
+            if (c >= CE) { c -= CE; ++r; if (r >= kMTileKeys) break; }
+            const int j = key0 + r;
+            bool need = j <= hi;
+            const __nv_bfloat16* src = p.pages;
+            if (need) {
+                int slot, off;
+                if (p.page_shift >= 0) { slot = j >> p.page_shift; off = j & (p.page_size - 1); }
+                else { slot = j / p.page_size; off = j - slot * p.page_size; }
+                if (slot != last_slot) { page = slot < p.table_width ? table[slot] : -1; last_slot = slot; }
+                if (page < 0 || page >= p.num_pages) {
+                    atomicExch(p.err, 4);                 // an entry a token of this block must see has no page
+                    need = false;
+                } else {
+                    src = p.pages + (((static_cast<int64_t>(page) * p.planes + plane) * p.G + kvh) * p.page_size + off) * E + c * 8;
+                }
+            }
+            cp_async16(dst + r * LD + c * 8, src, need);
+        }
+    };
+
+    load_tile(0, 0);
+    cp_async_commit();
+
+    // the two rows this thread owns in its warp's slab of 16
+    int ptok[2], lo_t[2], nb_t[2];
+    float b1[2] = {0.f, 0.f}, b2[2] = {0.f, 0.f};
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+        const int r = warp * 16 + (lane >> 2) + half * 8;
+        const int tok = min(r / g, n_tok - 1);            // rows past the block's tokens are never stored
+        const int head = kvh * g + r % g;
+        ptok[half] = pos_first + tok;
+        lo_t[half] = first_visible(ptok[half], p.mp);
+        nb_t[half] = visible_blocks(ptok[half], p.mp);
+        if (p.r1 != nullptr) { b1[half] = p.r1[head]; b2[half] = p.r2[head]; }
+        if (p.sink != nullptr) { m[half] = p.sink[head] * kLog2eM; l[half] = (lane & 3) == 0 ? 1.f : 0.f; }
+    }
+    const bool warp_has_rows = warp * 16 < n_tok * g;
+    const int warp_first_pos = pos_first + min(n_tok - 1, (warp * 16) / g);
+    const int warp_last_pos = pos_first + min(n_tok - 1, (warp * 16 + 15) / g);
+    const int warp_lo = first_visible(warp_first_pos, p.mp), warp_nb = visible_blocks(warp_last_pos, p.mp);
+    const float cap = p.mp.softcap, inv_cap = cap > 0.f ? 1.f / cap : 0.f;
+
+    float o[W / 8][4];
+#pragma unroll
+    for (int dt = 0; dt < W / 8; ++dt) { o[dt][0] = o[dt][1] = o[dt][2] = o[dt][3] = 0.f; }
+    uint32_t qf[W / 16][4];
+
+    for (int it = 0; it < n_tiles; ++it) {
+        if (it + 1 < n_tiles) load_tile(it + 1, (it + 1) & 1);
+        cp_async_commit();
+        const bool pooled = it < n_pool_tiles;
+        const int key0 = pooled ? it * kMTileKeys : (tok_tile0 + it - n_pool_tiles) * kMTileKeys;
+        cp_async_wait<1>();                               // everything but the newest group: the query tile and tile `it`
+        __syncthreads();
+        if (it == 0) {
+#pragma unroll
+            for (int ks = 0; ks < W / 16; ++ks) {
+                if (!EXACT && ks * 16 >= dk) break;
+                ldm_x4(qf[ks], sQ + (warp * 16 + (lane & 15)) * LDQ + ks * 16 + (lane >> 4) * 8);
+            }
+        }
+        const bool wanted = pooled ? key0 < warp_nb : (key0 <= warp_last_pos && key0 + kMTileKeys - 1 >= warp_lo);
+        if (warp_has_rows && wanted) {
+            const __nv_bfloat16* tile = sK + (it & 1) * kMTileKeys * LD;
+            float s[8][4];
+#pragma unroll
+            for (int nt = 0; nt < 8; ++nt) { s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f; }
+#pragma unroll
+            for (int ks = 0; ks < W / 16; ++ks) {
+                if (!EXACT && ks * 16 >= dk) break;
+#pragma unroll
+                for (int np = 0; np < 4; ++np) {
+                    uint32_t b[4];
+                    ldm_x4(b, tile + (np * 16 + (lane & 7) + ((lane >> 4) & 1) * 8) * LD + ks * 16 + ((lane >> 3) & 1) * 8);
+                    mma_16816(s[np * 2], qf[ks], b[0], b[1]);
+                    mma_16816(s[np * 2 + 1], qf[ks], b[2], b[3]);
+                }
+            }
+            // scale, cap, distance term, mask; running maximum
+            float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+            for (int nt = 0; nt < 8; ++nt) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int half = e >> 1;
+                    const int j = key0 + nt * 8 + ((lane & 3) << 1) + (e & 1);
+                    const bool visible = pooled ? j < nb_t[half] : (j >= lo_t[half] && j <= ptok[half]);
+                    float v = s[nt][e] * p.mp.scale;
+                    if (cap > 0.f) v = cap * tanh_by_exp(v * inv_cap);
+                    if (p.r1 != nullptr && !pooled) v -= b1[half] * __logf(1.f + b2[half] * static_cast<float>(max(ptok[half] - j, 0)));
+                    v = visible ? v * kLog2eM : -INFINITY;
+                    s[nt][e] = v;
+                    mx[half] = fmaxf(mx[half], v);
+                }
+            }
+            float corr[2];
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+                mx[half] = fmaxf(mx[half], __shfl_xor_sync(0xffffffffu, mx[half], 1));
+                mx[half] = fmaxf(mx[half], __shfl_xor_sync(0xffffffffu, mx[half], 2));
+                const float m_new = fmaxf(m[half], mx[half]);
+                corr[half] = (m[half] == -INFINITY) ? 0.f : ex2(m[half] - m_new);
+                m[half] = m_new;
+            }
+            float sum[2] = {0.f, 0.f};
+#pragma unroll
+            for (int nt = 0; nt < 8; ++nt) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int half = e >> 1;
+                    const float pj = (s[nt][e] == -INFINITY) ? 0.f : ex2(s[nt][e] - m[half]);
+                    s[nt][e] = pj;
+                    sum[half] += pj;
+                }
+            }
+#pragma unroll
+            for (int half = 0; half < 2; ++half) l[half] = l[half] * corr[half] + sum[half];
+#pragma unroll
+            for (int dt = 0; dt < W / 8; ++dt) {
+                o[dt][0] *= corr[0]; o[dt][1] *= corr[0]; o[dt][2] *= corr[1]; o[dt][3] *= corr[1];
+            }
+            // O += P V: the columns behind the keys, read transposed
+#pragma unroll
+            for (int kk = 0; kk < 4; ++kk) {
+                uint32_t a[4];
+                a[0] = pack2(s[kk * 2][0], s[kk * 2][1]);
+                a[1] = pack2(s[kk * 2][2], s[kk * 2][3]);
+                a[2] = pack2(s[kk * 2 + 1][0], s[kk * 2 + 1][1]);
+                a[3] = pack2(s[kk * 2 + 1][2], s[kk * 2 + 1][3]);
+#pragma unroll
+                for (int dp = 0; dp < W / 16; ++dp) {
+                    if (!EXACT && dp * 16 >= dv) break;
+                    uint32_t b[4];
+                    ldm_x4_trans(b, tile + (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LD + dk + dp * 16 + ((lane >> 4) & 1) * 8);
+                    mma_16816(o[dp * 2], a, b[0], b[1]);
+                    mma_16816(o[dp * 2 + 1], a, b[2], b[3]);
+                }
+            }
+        }
+        __syncthreads();                                  // the stage may be filled again
+    }
+
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+        l[half] += __shfl_xor_sync(0xffffffffu, l[half], 1);
+        l[half] += __shfl_xor_sync(0xffffffffu, l[half], 2);
+    }
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+        const int r = warp * 16 + (lane >> 2) + half * 8;
+        const int tok = r / g;
+        if (tok >= n_tok) continue;
+        const int head = kvh * g + r % g;
+        float inv = l[half] > 0.f ? 1.f / l[half] : 0.f;
+        if (p.gate != nullptr)
+            inv *= 1.f / (1.f + __expf(-__bfloat162float(p.gate[static_cast<int64_t>(cu0 + q0 + tok) * p.gate_stride + head])));
+        __nv_bfloat16* dst = p.out + (static_cast<int64_t>(cu0 + q0 + tok) * p.H + head) * dv;
+#pragma unroll
+        for (int dt = 0; dt < W / 8; ++dt) {
+            const int d = dt * 8 + ((lane & 3) << 1);
+            if (!EXACT && d >= dv) break;
+            *reinterpret_cast<__nv_bfloat162*>(dst + d) = __floats2bfloat162_rn(o[dt][half * 2] * inv, o[dt][half * 2 + 1] * inv);
+        }
+    }
+}
+
+template <int W, bool EXACT>
+int launch_attn_masked(const MaskedAttnParams& p, int num_tiles, cudaStream_t stream) {
+    const int E = p.dk + p.dv;
+    const size_t smem = (static_cast<size_t>(kMTileRows) * (p.dk + 8) + static_cast<size_t>(2) * kMTileKeys * (E + 8)) * sizeof(__nv_bfloat16);
+    static bool raised = false;
+    if (!raised) {
+        if (cudaFuncSetAttribute(attn_masked_kernel<W, EXACT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024) != cudaSuccess)
+            return launch_status();
+        raised = true;
+    }
+    launch_kernel(attn_masked_kernel<W, EXACT>, dim3(num_tiles, p.G), dim3(kMThreads), smem, stream, p);
+    return launch_status();
+}
+
 }  // namespace cvb
 
 using namespace cvb;
@@ -293,4 +568,46 @@ extern "C" int cvb_attn_masked_general(void* out, const void* q, const void* pag
     CVB_DISPATCH_DTYPE(dtype, CALL);
 #undef CALL
     return launch_status();
+}
+
+// 1 if the tensor-core kernel takes this shape: bf16, key and value sizes 16..128 in steps of 16, up to 64 query heads per kv head.
+extern "C" int cvb_attn_masked_supported(int H, int G, int dk, int dv) {
+    return (H > 0 && G > 0 && H % G == 0 && H / G <= kMTileRows && dk >= 16 && dk <= 128 && dk % 16 == 0
+            && dv >= 16 && dv <= 128 && dv % 16 == 0) ? 1 : 0;
+}
+
+extern "C" int cvb_attn_masked_bf16(void* out, const void* q, const void* pages, const int* block_tables, int table_width,
+                                    const int* cu_seqlens, const int* positions, int S, int num_tiles, int H, int G, int dk, int dv,
+                                    int page_size, int planes, int chunk, int window, int pool, float scale, float softcap,
+                                    const float* r1, const float* r2, const float* sink, const void* gate, int gate_stride,
+                                    int num_pages, int* err_flag, cudaStream_t stream) {
+    if (num_tiles == 0 || S == 0) return CVB_OK;
+    if (S < 0 || num_tiles < 0 || page_size <= 0 || table_width <= 0 || num_pages <= 0) return CVB_E_SIZE;
+    if (!cvb_attn_masked_supported(H, G, dk, dv)) return CVB_E_UNSUPPORTED;
+    if (chunk < 0 || window < 0 || pool < 0 || (planes != 1 && planes != 2) || (pool > 0 && (planes != 2 || window <= 0))) return CVB_E_SHAPE;
+    if ((r1 == nullptr) != (r2 == nullptr)) return CVB_E_SHAPE;
+    if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(pages) | reinterpret_cast<uintptr_t>(out)) & 15) return CVB_E_ALIGN;
+    if (G > 65535) return CVB_E_SIZE;
+    MaskedAttnParams p;
+    p.out = static_cast<__nv_bfloat16*>(out);
+    p.q = static_cast<const __nv_bfloat16*>(q);
+    p.pages = static_cast<const __nv_bfloat16*>(pages);
+    p.gate = static_cast<const __nv_bfloat16*>(gate); p.gate_stride = gate_stride;
+    p.r1 = r1; p.r2 = r2; p.sink = sink;
+    p.block_tables = block_tables; p.cu_seqlens = cu_seqlens; p.positions = positions;
+    p.table_width = table_width; p.S = S; p.H = H; p.G = G; p.dk = dk; p.dv = dv; p.page_size = page_size;
+    p.num_pages = num_pages; p.planes = planes;
+    p.page_shift = -1;
+    for (int sh = 0; sh < 31; ++sh)
+        if ((1 << sh) == page_size) p.page_shift = sh;
+    p.mp = MaskParams{chunk, window, pool, scale, softcap};
+    p.err = err_flag;
+    const int w = dk > dv ? dk : dv;
+    const bool exact = dk == dv && (dk == 64 || dk == 128);
+#define CVB_MASKED_WIDTH(WW)                                                                                             \
+    if (w <= WW) return exact ? launch_attn_masked<WW, true>(p, num_tiles, stream) : launch_attn_masked<WW, false>(p, num_tiles, stream);
+    CVB_MASKED_WIDTH(64)
+    CVB_MASKED_WIDTH(128)
+#undef CVB_MASKED_WIDTH
+    return CVB_E_UNSUPPORTED;
 }

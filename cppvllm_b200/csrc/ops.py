@@ -997,7 +997,7 @@ def _attn_masked_lib():
     global _attn_masked
     if _attn_masked is None:
         lib = load_library("attn_masked")
-        for name in ("cvb_masked_qkv_prep", "cvb_pool_entries", "cvb_attn_masked_general"):
+        for name in ("cvb_masked_qkv_prep", "cvb_pool_entries", "cvb_attn_masked_general", "cvb_attn_masked_bf16"):
             getattr(lib, name).restype = c_int
         _attn_masked = lib
     return _attn_masked
@@ -1088,6 +1088,42 @@ def attn_masked_general(out: torch.Tensor, q: torch.Tensor, pages: torch.Tensor,
         c_int(pool), c_float(scale), c_float(softcap), _ptr(r1), _ptr(r2), _ptr(sink), _ptr(gate),
         c_int(gate.stride(0) if gate is not None else 0), c_int(num_pages), c_int(dtype_code(q.dtype)),
         _ptr(error_flag(q.device)), _stream()), "attn_masked_general")
+    return out
+
+
+
+def attn_masked_supported(dtype: torch.dtype, num_heads: int, num_kv_heads: int, dim: int, vdim: int) -> bool:
+    """Whether the tensor-core kernel takes the shape (csrc/attention_masked.cu): bf16, key and value sizes 16 to 128 in steps
+    of 16, up to 64 query heads per kv head."""
+    return (dtype == torch.bfloat16 and dim % 16 == 0 and 16 <= dim <= 128 and vdim % 16 == 0 and 16 <= vdim <= 128
+            and num_kv_heads > 0 and num_heads % num_kv_heads == 0 and num_heads // num_kv_heads <= 64)
+
+
+def attn_masked_bf16(out: torch.Tensor, q: torch.Tensor, pages: torch.Tensor, block_tables: torch.Tensor, cu_seqlens: torch.Tensor,
+                     positions: torch.Tensor, num_seqs: int, num_tiles: int, num_heads: int, num_kv_heads: int, dim: int, vdim: int,
+                     page_size: int, scale: float, planes: int = 1, chunk: int = 0, window: int = 0, pool: int = 0,
+                     softcap: float = 0.0, r1: Optional[torch.Tensor] = None, r2: Optional[torch.Tensor] = None,
+                     sink: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """The tensor-core form of attn_masked_general for prompt portions and decoded tokens alike; `num_tiles` as
+    attn_keys_tiles gives it (blocks of 64 // group tokens of one request)."""
+    _cuda(out, q, pages, block_tables, cu_seqlens, positions, r1, r2, sink, gate)
+    _contig(out, q, pages, block_tables, cu_seqlens, positions, r1, r2, sink)
+    H = num_heads
+    if q.dtype != torch.bfloat16 or pages.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
+        raise KernelError("attn_masked_bf16 takes bf16 queries, pages and output")
+    if block_tables.dtype != torch.int32 or block_tables.dim() != 2 or cu_seqlens.dtype != torch.int32 or positions.dtype != torch.int32:
+        raise KernelError("attn_masked_bf16: block_tables [S, W], cu_seqlens and positions must be int32")
+    for t in (r1, r2, sink):
+        if t is not None and (t.dtype != torch.float32 or t.numel() != H):
+            raise KernelError("attn_masked_bf16: r1, r2 and sink are float32 [H]")
+    if gate is not None and (gate.dtype != torch.bfloat16 or gate.shape[1] != H or gate.stride(1) != 1):
+        raise KernelError("attn_masked_bf16: gate bf16 [T, H]")
+    num_pages = pages.numel() // (planes * num_kv_heads * page_size * (dim + vdim))
+    _check(_attn_masked_lib().cvb_attn_masked_bf16(
+        _ptr(out), _ptr(q), _ptr(pages), _ptr(block_tables), c_int(block_tables.shape[1]), _ptr(cu_seqlens), _ptr(positions),
+        c_int(num_seqs), c_int(num_tiles), c_int(H), c_int(num_kv_heads), c_int(dim), c_int(vdim), c_int(page_size), c_int(planes),
+        c_int(chunk), c_int(window), c_int(pool), c_float(scale), c_float(softcap), _ptr(r1), _ptr(r2), _ptr(sink), _ptr(gate),
+        c_int(gate.stride(0) if gate is not None else 0), c_int(num_pages), _ptr(error_flag(q.device)), _stream()), "attn_masked_bf16")
     return out
 
 

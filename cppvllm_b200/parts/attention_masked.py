@@ -128,6 +128,13 @@ class MaskedAttention(Mixer):
 
     def attend(self, att, q, gate, ctx, cache, g):
         H, G, dk, dv = self.num_heads, self.num_kv_heads, self.dim, self.vdim
+        if not self.force_general and ops.attn_masked_supported(q.dtype, H, G, dk, dv):
+            q_lens = ctx.q_lens if ctx.q_lens is not None else [1] * ctx.num_seqs
+            ops.attn_masked_bf16(att, q, cache.pages, g.block_tables, ctx.cu_seqlens, ctx.positions, ctx.num_seqs,
+                                 ops.attn_keys_tiles(q_lens, H, G), H, G, dk, dv, g.page_size, self.scale, planes=self.planes,
+                                 chunk=self.chunk, window=self.window, pool=self.pool, softcap=self.softcap, r1=self.r1, r2=self.r2,
+                                 sink=self.sinks, gate=gate)
+            return
         ops.attn_masked_general(att, q, cache.pages, g.block_tables, ctx.seq_of_token, ctx.positions, ctx.num_tokens, H, G, dk, dv,
                                 g.page_size, self.scale, planes=self.planes, chunk=self.chunk, window=self.window, pool=self.pool,
                                 softcap=self.softcap, r1=self.r1, r2=self.r2, sink=self.sinks, gate=gate)

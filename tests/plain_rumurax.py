@@ -217,11 +217,16 @@ def expert(z, w, p, rnd=identity):
     return rnd(a @ w[p + "down"].T)
 
 
-def routed_experts(h, w, p, f, rnd=identity):
+def routed_experts(h, w, p, f, rnd=identity, margins=None):
+    """`margins` (a list) receives, per token, how far the last chosen expert's router logit lies above the first one left out."""
     T = h.shape[0]
     E, top = f["router"]["experts"], f["router"]["top"]
-    s = torch.sigmoid(h @ w[p + "router"].T)                                    # [T, E]
+    z = h @ w[p + "router"].T
+    s = torch.sigmoid(z)                                                        # [T, E]
     best = torch.topk(s, top, dim=1)
+    if margins is not None:
+        ordered = torch.sort(z, dim=1, descending=True).values
+        margins.append(ordered[:, top - 1] - ordered[:, top] if top < E else torch.full((T,), math.inf, dtype=F))
     y = torch.zeros_like(h)
     for t in range(T):
         for c in range(top):
@@ -245,7 +250,7 @@ def forward(model_dir: str, tokens, rnd=identity, return_layers: bool = False):
     return forward_loaded(cfg, w, tokens, rnd, return_layers)
 
 
-def forward_loaded(cfg, w, tokens, rnd=identity, return_layers: bool = False):
+def forward_loaded(cfg, w, tokens, rnd=identity, return_layers: bool = False, router_margins=None):
     eps, S = cfg["norm"]["eps"], cfg.get("streams", 1)
     tokens = torch.as_tensor(tokens, dtype=torch.long)
     X = w["embed"][tokens][:, None, :].repeat(1, S, 1)                          # [T, S, D]
@@ -275,7 +280,7 @@ def forward_loaded(cfg, w, tokens, rnd=identity, return_layers: bool = False):
             v_first = kept["v"]
         f = layer.get("mlp")
         if f is not None:
-            ff = lambda h, f=f, p=p: routed_experts(h, w, p + "mlp.", f, rnd)   # noqa: E731
+            ff = lambda h, f=f, p=p: routed_experts(h, w, p + "mlp.", f, rnd, router_margins)   # noqa: E731
             if S > 1 or (p + "hc2.in") in w:
                 X = stream_sublayer(X, w, p + "hc2.", w[p + "norm2"], eps, ff, rnd)
             else:
