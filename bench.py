@@ -21,7 +21,7 @@ sizes, batch 8, context 4096 (the last timed step runs at 4096 tokens per reques
                the Qwen3-8B layer sizes (contexts 4096 and 8192) and a mixed step at the Qwen3-32B layer sizes (64
                decoding requests at context 4096 beside a 1,024-token portion of a 2,048-token prompt), both with fewer
                layers than the models have (the number is named beside them), each with its fraction of the peak.
-`--design givirax` (or `dugulorn`, `lorulix`) runs another measurement instead and leaves the above untouched: that design beside Qwen3 at equal
+`--design givirax` (or `dugulorn`, `lorulix`, `rumurax`) runs another measurement instead and leaves the above untouched: that design beside Qwen3 at equal
 layer sizes, whole models (prefill, decode) and single kernels in pairs, one JSON line (cppvllm_b200/design_bench.py).
 Peaks come from MEASURED_PEAKS.json next to this file when the driver wrote it, else from the fallback
 (6650 GB/s, 1590 TFLOP/s).  Every timed step reads several GB, far more than the 126 MB L2.
@@ -344,7 +344,7 @@ def main():
     ap.add_argument("--no-points", action="store_true", help="the headline numbers only: no further batches, shapes or workloads")
     ap.add_argument("--no-larger-shapes", action="store_true", help="skip the points at the 8B and 32B layer sizes")
     ap.add_argument("--shape", default="0.6b", choices=["0.6b", "8b"], help="layer sizes of the headline run: Qwen3-0.6B (default) or Qwen3-8B")
-    ap.add_argument("--design", default="", choices=["", "givirax", "dugulorn", "lorulix"],
+    ap.add_argument("--design", default="", choices=["", "givirax", "dugulorn", "lorulix", "rumurax"],
                     help="instead of the headline workload: this design beside the closest existing model at equal layer sizes "
                          "(whole models and single kernels; see cppvllm_b200/design_bench.py)")
     ap.add_argument("--design-sizes", default="small,large")

@@ -38,6 +38,103 @@ namespace cvb {
 
 constexpr int kPrepWarps = 4;
 
+__device__ __forceinline__ float2 load2(const float* p) { return *reinterpret_cast<const float2*>(p); }
+__device__ __forceinline__ float2 load2(const __nv_bfloat16* p) { return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(p)); }
+__device__ __forceinline__ void store2(float* p, float2 v) { *reinterpret_cast<float2*>(p) = v; }
+__device__ __forceinline__ void store2(__nv_bfloat16* p, float2 v) { *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(v.x, v.y); }
+
+constexpr int kPrepPairs = 8;                            // pairs per lane: heads of up to 512 elements
+
+// The same epilogue two elements at a time, for even sizes and a rotation in pairs (2i, 2i + 1) (or none): a lane holds whole
+// pairs in registers from the load to the store, so neither shared memory nor a second pass is needed.
+template <typename T>
+__global__ void __launch_bounds__(kPrepWarps * 32)
+masked_qkv_prep_pairs_kernel(T* __restrict__ q_out, const T* __restrict__ packed, int stride, const float* __restrict__ q_w,
+                             const float* __restrict__ k_w, const float* __restrict__ cos_t, const float* __restrict__ sin_t,
+                             const int* __restrict__ positions, const int* __restrict__ slots, T* __restrict__ pages,
+                             T* __restrict__ vfirst_out, const T* __restrict__ vfirst_in, const float* __restrict__ lam_p,
+                             int H, int G, int dk, int dv, int rot, int planes, int page_size, int max_pos, float eps,
+                             int64_t total_slots, int* __restrict__ err) {
+    pdl_trigger();
+    pdl_wait();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int task = blockIdx.y * kPrepWarps + warp;
+    if (task >= H + 2 * G) return;
+    const int64_t t = blockIdx.x;
+    const T* row = packed + t * stride;
+    const int slot = slots != nullptr ? slots[t] : -1;
+    const int ew = dk + dv;
+    int64_t entry = -1;
+    if (slot >= 0 && pages != nullptr) {
+        if (slot >= total_slots) {
+            if (lane == 0) atomicExch(err, 2);
+        } else {
+            const int64_t page = slot / page_size, off = slot % page_size;
+            entry = ((page * planes * G) * page_size + off) * ew;
+        }
+    }
+    if (task >= H + G) {                                // a value head
+        const int g = task - H - G;
+        const T* src = row + H * dk + G * dk + g * dv;
+        const float lam = (vfirst_in != nullptr && lam_p != nullptr) ? lam_p[0] : 0.f;
+        for (int e = lane * 2; e < dv; e += 64) {
+            float2 v = load2(src + e);
+            if (vfirst_out != nullptr) store2(vfirst_out + t * G * dv + g * dv + e, v);
+            if (vfirst_in != nullptr) {
+                const float2 f = load2(vfirst_in + t * G * dv + g * dv + e);
+                v.x = (1.f - lam) * v.x + lam * f.x;
+                v.y = (1.f - lam) * v.y + lam * f.y;
+            }
+            if (entry >= 0) store2(pages + entry + static_cast<int64_t>(g) * page_size * ew + dk + e, v);
+        }
+        return;
+    }
+    const bool is_q = task < H;
+    if (!is_q && entry < 0) return;
+    const T* src = is_q ? row + task * dk : row + H * dk + (task - H) * dk;
+    const float* w = is_q ? q_w : k_w;
+    const int np = dk >> 1, half = rot >> 1;
+    float2 x[kPrepPairs];
+    float ss = 0.f;
+#pragma unroll
+    for (int k = 0; k < kPrepPairs; ++k) {
+        const int i = lane + 32 * k;
+        if (i < np) { x[k] = load2(src + 2 * i); ss = fmaf(x[k].x, x[k].x, ss); ss = fmaf(x[k].y, x[k].y, ss); }
+    }
+    if (w != nullptr) {
+        ss = warp_sum(ss);
+        const float inv = rsqrtf(ss / static_cast<float>(dk) + eps);
+#pragma unroll
+        for (int k = 0; k < kPrepPairs; ++k) {
+            const int i = lane + 32 * k;
+            if (i < np) { x[k].x = x[k].x * inv * w[2 * i]; x[k].y = x[k].y * inv * w[2 * i + 1]; }
+        }
+    }
+    T* dst = is_q ? q_out + (t * H + task) * dk : pages + entry + static_cast<int64_t>(task - H) * page_size * ew;
+    const float* c_row = nullptr;
+    const float* s_row = nullptr;
+    if (cos_t != nullptr && half > 0) {
+        int pos = positions[t];
+        if (pos < 0 || pos >= max_pos) {
+            if (lane == 0) atomicExch(err, 3);
+            pos = pos < 0 ? 0 : max_pos - 1;
+        }
+        c_row = cos_t + static_cast<int64_t>(pos) * half;
+        s_row = sin_t + static_cast<int64_t>(pos) * half;
+    }
+#pragma unroll
+    for (int k = 0; k < kPrepPairs; ++k) {
+        const int i = lane + 32 * k;
+        if (i >= np) break;
+        float2 v = x[k];
+        if (c_row != nullptr && i < half) {
+            const float c = c_row[i], s = s_row[i];
+            v = make_float2(x[k].x * c - x[k].y * s, x[k].y * c + x[k].x * s);
+        }
+        store2(dst + 2 * i, v);
+    }
+}
+
 template <typename T>
 __global__ void __launch_bounds__(kPrepWarps * 32)
 masked_qkv_prep_kernel(T* __restrict__ q_out, const T* __restrict__ packed, int stride, const float* __restrict__ q_w,
@@ -120,6 +217,7 @@ pool_entries_kernel(T* __restrict__ pages, const int* __restrict__ block_tables,
                     const int* __restrict__ positions, int G, int ew, int pool, int page_size, int num_pages, int* __restrict__ err) {
     pdl_trigger();
     pdl_wait();
+    __shared__ int64_t off[128];                        // where the entries of up to 128 of the block's positions start
     const int64_t t = blockIdx.x;
     const int g = blockIdx.y;
     const int p = positions[t];
@@ -128,15 +226,32 @@ pool_entries_kernel(T* __restrict__ pages, const int* __restrict__ block_tables,
     const int* table = block_tables + static_cast<int64_t>(seq_of_token[t]) * table_width;
     const int dst_page = b / page_size < table_width ? table[b / page_size] : -1;
     if (dst_page < 0 || dst_page >= num_pages) { if (threadIdx.x == 0) atomicExch(err, 4); return; }
-    const float inv = 1.f / static_cast<float>(pool);
-    for (int e = threadIdx.x; e < ew; e += blockDim.x) {
-        float sum = 0.f;
-        for (int j = p - pool + 1; j <= p; ++j) {
+    float sum[4] = {0.f, 0.f, 0.f, 0.f};               // entries of up to 512 elements: four per thread
+    for (int j0 = p - pool + 1; j0 <= p; j0 += 128) {
+        const int n = min(128, p - j0 + 1);
+        __syncthreads();
+        if (threadIdx.x < n) {
+            const int j = j0 + threadIdx.x;
             const int page = j / page_size < table_width ? table[j / page_size] : -1;
-            if (page < 0 || page >= num_pages) { atomicExch(err, 4); continue; }
-            sum += to_float(pages[(((static_cast<int64_t>(page) * 2 + 0) * G + g) * page_size + j % page_size) * ew + e]);
+            if (page < 0 || page >= num_pages) { atomicExch(err, 4); off[threadIdx.x] = -1; }
+            else off[threadIdx.x] = (((static_cast<int64_t>(page) * 2 + 0) * G + g) * page_size + j % page_size) * ew;
         }
-        pages[(((static_cast<int64_t>(dst_page) * 2 + 1) * G + g) * page_size + b % page_size) * ew + e] = from_float<T>(sum * inv);
+        __syncthreads();
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const int e = threadIdx.x + k * 128;
+            if (e >= ew) break;
+            float acc = sum[k];
+#pragma unroll 8
+            for (int i = 0; i < n; ++i) acc += off[i] >= 0 ? to_float(pages[off[i] + e]) : 0.f;     // rising positions, one sum
+            sum[k] = acc;
+        }
+    }
+    const int64_t dst = (((static_cast<int64_t>(dst_page) * 2 + 1) * G + g) * page_size + b % page_size) * ew;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const int e = threadIdx.x + k * 128;
+        if (e < ew) pages[dst + e] = from_float<T>(sum[k] / static_cast<float>(pool));
     }
 }
 
@@ -262,6 +377,10 @@ struct MaskedAttnParams {
     const int* positions;               // [T]
     int gate_stride, table_width, S, H, G, dk, dv, page_size, page_shift, num_pages, planes;
     MaskParams mp;
+    // decode form only: the tiles of a (request, kv head) are shared out among `splits` blocks (gridDim.z); with more than
+    // one, a block leaves its part (unnormalised rows, maxima, sums) in `parts` and a second kernel merges them
+    int splits;
+    float* parts;                       // [S, G, splits, 16, dv + 2]
     int* err;
 };
 
@@ -507,6 +626,298 @@ int launch_attn_masked(const MaskedAttnParams& p, int num_tiles, cudaStream_t st
     return launch_status();
 }
 
+// ---- decoded tokens: one token per request ---------------------------------------------------------------------------
+//
+// A block owns one (request, kv head): the g <= 16 query heads of the group are the rows of ONE 16-row slab, and each of
+// the block's warps takes every n-th tile of 32 entries (first the pooled blocks the token sees, then its tokens from the
+// first visible one) into two stages of its own: cp.async by its own lanes, __syncwarp, no block-wide barrier in the loop.
+// The warps' parts are merged through shared memory; when few (request, kv head) pairs would leave SMs idle the tiles are
+// shared out among `splits` blocks as well, which leave their parts in scratch for a merge kernel.  The sink and the gate
+// join where the parts are merged, once.
+constexpr int kMDecKeys = 32;
+
+__device__ __forceinline__ void masked_finish(const MaskedAttnParams& p, int t, int head, int d, int dv, float mm, float ll, float acc) {
+    if (p.sink != nullptr) {
+        const float sk = p.sink[head] * kLog2eM;
+        const float top = fmaxf(mm, sk);
+        const float f = mm == -INFINITY ? 0.f : ex2(mm - top);
+        ll = ll * f + ex2(sk - top);
+        acc *= f;
+    }
+    float v = ll > 0.f ? acc / ll : 0.f;
+    if (p.gate != nullptr) v *= 1.f / (1.f + __expf(-__bfloat162float(p.gate[static_cast<int64_t>(t) * p.gate_stride + head])));
+    p.out[(static_cast<int64_t>(t) * p.H + head) * dv + d] = __float2bfloat16_rn(v);
+}
+
+template <int W, bool EXACT>
+__global__ void __launch_bounds__(256)
+attn_masked_decode_kernel(const MaskedAttnParams p) {
+    pdl_trigger();
+    pdl_wait();
+    const int dk = EXACT ? W : p.dk, dv = EXACT ? W : p.dv;
+    const int E = dk + dv;
+    const int LDQ = dk + 8, LD = E + 8;
+    const int CQ = dk >> 3, CE = E >> 3;
+    const int nw = blockDim.x >> 5;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    __nv_bfloat16* sQ = reinterpret_cast<__nv_bfloat16*>(smem_raw);                    // [16][LDQ]
+    __nv_bfloat16* sK = sQ + 16 * LDQ;                                                 // [warps][2][32][LD]
+    float* red_ml = reinterpret_cast<float*>(sK + nw * 2 * kMDecKeys * LD);            // [warps][16][2]
+    const int g = p.H / p.G;
+    const int seq = blockIdx.x, kvh = blockIdx.y;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int t = p.cu_seqlens[seq];
+    const int pos = p.positions[t];
+    const int* table = p.block_tables + static_cast<int64_t>(seq) * p.table_width;
+    const int lo = first_visible(pos, p.mp), nb = visible_blocks(pos, p.mp);
+    const int n_pool_tiles = (nb + kMDecKeys - 1) / kMDecKeys;
+    const int tok_tile0 = lo / kMDecKeys;
+    const int n_tiles = n_pool_tiles + pos / kMDecKeys - tok_tile0 + 1;
+
+    for (int i = threadIdx.x; i < 16 * CQ; i += blockDim.x) {
+        const int r = i / CQ, c = i - r * CQ;
+        const bool valid = r < g;
+        cp_async16(sQ + r * LDQ + c * 8, valid ? p.q + (static_cast<int64_t>(t) * p.H + kvh * g + r) * dk + c * 8 : p.q, valid);
+    }
+    cp_async_commit();
+
+    __nv_bfloat16* my = sK + warp * 2 * kMDecKeys * LD;
+    const int ld_r0 = lane / CE, ld_c0 = lane - ld_r0 * CE;
+    const int ld_dr = 32 / CE, ld_dc = 32 - ld_dr * CE;
+    auto load_tile = [&](int it, int stage) {
+        const bool pooled = it < n_pool_tiles;
+        const int key0 = pooled ? it * kMDecKeys : (tok_tile0 + it - n_pool_tiles) * kMDecKeys;
+        const int hi = pooled ? nb - 1 : pos;
+        const int plane = pooled ? 1 : 0;
+        __nv_bfloat16* dst = my + stage * kMDecKeys * LD;
+        int last_slot = -1, page = -1;
+        const __nv_bfloat16* page_base = p.pages;
+        int r = ld_r0, c = ld_c0;                         // chunk lane + 32 n is row (lane + 32 n) / CE: kept by increments
+        for (; r < kMDecKeys; r += ld_dr, c += ld_dc) {
+            if (c >= CE) { c -= CE; ++r; if (r >= kMDecKeys) break; }
+            const int j = key0 + r;
+            bool need = j <= hi;
+            const __nv_bfloat16* src = p.pages;
+            if (need) {
+                int slot, off;
+                if (p.page_shift >= 0) { slot = j >> p.page_shift; off = j & (p.page_size - 1); }
+                else { slot = j / p.page_size; off = j - slot * p.page_size; }
+                if (slot != last_slot) {
+                    page = slot < p.table_width ? table[slot] : -1;
+                    last_slot = slot;
+                    page_base = p.pages + ((static_cast<int64_t>(page) * p.planes + plane) * p.G + kvh) * p.page_size * E;
+                }
+                if (page < 0 || page >= p.num_pages) {
+                    atomicExch(p.err, 4);
+                    need = false;
+                } else {
+                    src = page_base + off * E + c * 8;
+                }
+            }
+            cp_async16(dst + r * LD + c * 8, src, need);
+        }
+    };
+
+    const int lanes_w = nw * p.splits;                    // warps that share the tiles: this block's and its siblings'
+    const int gw = blockIdx.z * nw + warp;
+    const int my_tiles = n_tiles > gw ? (n_tiles - gw + lanes_w - 1) / lanes_w : 0;     // tiles gw, gw + lanes_w, ...
+    if (my_tiles > 0) load_tile(gw, 0);
+    cp_async_commit();
+    cp_async_wait<1>();                                   // this thread's share of the queries
+    __syncthreads();                                      // everybody's share
+    uint32_t qf[W / 16][4];
+#pragma unroll
+    for (int ks = 0; ks < W / 16; ++ks) {
+        if (!EXACT && ks * 16 >= dk) break;
+        ldm_x4(qf[ks], sQ + (lane & 15) * LDQ + ks * 16 + (lane >> 4) * 8);
+    }
+    float b1[2] = {0.f, 0.f}, b2[2] = {0.f, 0.f};
+    if (p.r1 != nullptr) {
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            const int r = min((lane >> 2) + half * 8, g - 1);   // rows past the group repeat its last head; never stored
+            b1[half] = p.r1[kvh * g + r];
+            b2[half] = p.r2[kvh * g + r];
+        }
+    }
+    const float cap = p.mp.softcap, inv_cap = cap > 0.f ? 1.f / cap : 0.f;
+
+    float o[W / 8][4];
+#pragma unroll
+    for (int dt = 0; dt < W / 8; ++dt) { o[dt][0] = o[dt][1] = o[dt][2] = o[dt][3] = 0.f; }
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+
+    for (int n = 0; n < my_tiles; ++n) {
+        const int it = gw + n * lanes_w;
+        if (n + 1 < my_tiles) load_tile(it + lanes_w, (n + 1) & 1);
+        cp_async_commit();
+        cp_async_wait<1>();
+        __syncwarp();
+        const bool pooled = it < n_pool_tiles;
+        const int key0 = pooled ? it * kMDecKeys : (tok_tile0 + it - n_pool_tiles) * kMDecKeys;
+        const __nv_bfloat16* tile = my + (n & 1) * kMDecKeys * LD;
+        float s[kMDecKeys / 8][4];
+#pragma unroll
+        for (int nt = 0; nt < kMDecKeys / 8; ++nt) { s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f; }
+#pragma unroll
+        for (int ks = 0; ks < W / 16; ++ks) {
+            if (!EXACT && ks * 16 >= dk) break;
+#pragma unroll
+            for (int np = 0; np < kMDecKeys / 16; ++np) {
+                uint32_t b[4];
+                ldm_x4(b, tile + (np * 16 + (lane & 7) + ((lane >> 4) & 1) * 8) * LD + ks * 16 + ((lane >> 3) & 1) * 8);
+                mma_16816(s[np * 2], qf[ks], b[0], b[1]);
+                mma_16816(s[np * 2 + 1], qf[ks], b[2], b[3]);
+            }
+        }
+        float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+        for (int nt = 0; nt < kMDecKeys / 8; ++nt) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int half = e >> 1;
+                const int j = key0 + nt * 8 + ((lane & 3) << 1) + (e & 1);
+                const bool visible = pooled ? j < nb : (j >= lo && j <= pos);
+                float v = s[nt][e] * p.mp.scale;
+                if (cap > 0.f) v = cap * tanh_by_exp(v * inv_cap);
+                if (p.r1 != nullptr && !pooled) v -= b1[half] * __logf(1.f + b2[half] * static_cast<float>(max(pos - j, 0)));
+                v = visible ? v * kLog2eM : -INFINITY;
+                s[nt][e] = v;
+                mx[half] = fmaxf(mx[half], v);
+            }
+        }
+        float corr[2];
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            mx[half] = fmaxf(mx[half], __shfl_xor_sync(0xffffffffu, mx[half], 1));
+            mx[half] = fmaxf(mx[half], __shfl_xor_sync(0xffffffffu, mx[half], 2));
+            const float m_new = fmaxf(m[half], mx[half]);
+            corr[half] = (m[half] == -INFINITY) ? 0.f : ex2(m[half] - m_new);
+            m[half] = m_new;
+        }
+        float sum[2] = {0.f, 0.f};
+#pragma unroll
+        for (int nt = 0; nt < kMDecKeys / 8; ++nt) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float pj = (s[nt][e] == -INFINITY) ? 0.f : ex2(s[nt][e] - m[e >> 1]);
+                s[nt][e] = pj;
+                sum[e >> 1] += pj;
+            }
+        }
+#pragma unroll
+        for (int half = 0; half < 2; ++half) l[half] = l[half] * corr[half] + sum[half];
+        if (__any_sync(0xffffffffu, corr[0] != 1.f || corr[1] != 1.f)) {     // no row's maximum moved: nothing to rescale
+#pragma unroll
+            for (int dt = 0; dt < W / 8; ++dt) {
+                o[dt][0] *= corr[0]; o[dt][1] *= corr[0]; o[dt][2] *= corr[1]; o[dt][3] *= corr[1];
+            }
+        }
+#pragma unroll
+        for (int kk = 0; kk < kMDecKeys / 16; ++kk) {
+            uint32_t a[4];
+            a[0] = pack2(s[kk * 2][0], s[kk * 2][1]);
+            a[1] = pack2(s[kk * 2][2], s[kk * 2][3]);
+            a[2] = pack2(s[kk * 2 + 1][0], s[kk * 2 + 1][1]);
+            a[3] = pack2(s[kk * 2 + 1][2], s[kk * 2 + 1][3]);
+#pragma unroll
+            for (int dp = 0; dp < W / 16; ++dp) {
+                if (!EXACT && dp * 16 >= dv) break;
+                uint32_t b[4];
+                ldm_x4_trans(b, tile + (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LD + dk + dp * 16 + ((lane >> 4) & 1) * 8);
+                mma_16816(o[dp * 2], a, b[0], b[1]);
+                mma_16816(o[dp * 2 + 1], a, b[2], b[3]);
+            }
+        }
+        __syncwarp();                                     // the stage may be filled again
+    }
+    cp_async_wait<0>();
+
+    // merge the warps' parts: each leaves its sums, maxima and its accumulator [16][dv] (float) in its own stages
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+        l[half] += __shfl_xor_sync(0xffffffffu, l[half], 1);
+        l[half] += __shfl_xor_sync(0xffffffffu, l[half], 2);
+    }
+    __syncwarp();
+    float* part = reinterpret_cast<float*>(my);            // 16 * dv floats = 64 * dv bytes, within the warp's two stages (128 * LD bytes)
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+        const int r = (lane >> 2) + half * 8;
+        if ((lane & 3) == 0) { red_ml[(warp * 16 + r) * 2] = m[half]; red_ml[(warp * 16 + r) * 2 + 1] = l[half]; }
+#pragma unroll
+        for (int dt = 0; dt < W / 8; ++dt) {
+            const int d = dt * 8 + ((lane & 3) << 1);
+            if (!EXACT && d >= dv) break;
+            part[r * dv + d] = o[dt][half * 2];
+            part[r * dv + d + 1] = o[dt][half * 2 + 1];
+        }
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < g * dv; i += blockDim.x) {
+        const int r = i / dv, d = i - r * dv;
+        float mm = -INFINITY;
+        for (int w = 0; w < nw; ++w) mm = fmaxf(mm, red_ml[(w * 16 + r) * 2]);
+        float ll = 0.f, acc = 0.f;
+        for (int w = 0; w < nw; ++w) {
+            const float mw = red_ml[(w * 16 + r) * 2];
+            const float f = mw == -INFINITY ? 0.f : ex2(mw - mm);
+            ll += red_ml[(w * 16 + r) * 2 + 1] * f;
+            acc += reinterpret_cast<const float*>(sK + w * 2 * kMDecKeys * LD)[r * dv + d] * f;
+        }
+        if (p.splits == 1) {
+            masked_finish(p, t, kvh * g + r, d, dv, mm, ll, acc);
+        } else {
+            float* dst = p.parts + ((static_cast<int64_t>(seq) * p.G + kvh) * p.splits + blockIdx.z) * 16 * (dv + 2) + r * (dv + 2);
+            dst[d] = acc;
+            if (d == 0) { dst[dv] = mm; dst[dv + 1] = ll; }
+        }
+    }
+}
+
+// out = the parts of a (request, kv head) added up: rows scaled to the common maximum, divided by the common sum
+__global__ void attn_masked_merge_kernel(const MaskedAttnParams p) {
+    pdl_trigger();
+    pdl_wait();
+    const int g = p.H / p.G, dv = p.dv;
+    const int seq = blockIdx.x, kvh = blockIdx.y;
+    const int t = p.cu_seqlens[seq];
+    const float* base = p.parts + (static_cast<int64_t>(seq) * p.G + kvh) * p.splits * 16 * (dv + 2);
+    for (int i = blockIdx.z * blockDim.x + threadIdx.x; i < g * dv; i += gridDim.z * blockDim.x) {
+        const int r = i / dv, d = i - r * dv;
+        float mm = -INFINITY;
+        for (int z = 0; z < p.splits; ++z) mm = fmaxf(mm, base[(z * 16 + r) * (dv + 2) + dv]);
+        float ll = 0.f, acc = 0.f;
+        for (int z = 0; z < p.splits; ++z) {
+            const float* row = base + (z * 16 + r) * (dv + 2);
+            const float f = row[dv] == -INFINITY ? 0.f : ex2(row[dv] - mm);
+            ll += row[dv + 1] * f;
+            acc += row[d] * f;
+        }
+        masked_finish(p, t, kvh * g + r, d, dv, mm, ll, acc);
+    }
+}
+
+template <int W, bool EXACT>
+int launch_attn_masked_decode(const MaskedAttnParams& p, cudaStream_t stream) {
+    const int E = p.dk + p.dv;
+    // as many warps as their stages leave room for, eight at most
+    const size_t per_warp = static_cast<size_t>(2) * kMDecKeys * (E + 8) * sizeof(__nv_bfloat16) + 16 * 2 * sizeof(float);
+    const size_t room = 216 * 1024 - static_cast<size_t>(16) * (p.dk + 8) * sizeof(__nv_bfloat16);
+    const int nw = room / per_warp >= 8 ? 8 : static_cast<int>(room / per_warp);
+    const size_t smem = (static_cast<size_t>(16) * (p.dk + 8) + static_cast<size_t>(nw) * 2 * kMDecKeys * (E + 8)) * sizeof(__nv_bfloat16)
+                        + nw * 16 * 2 * sizeof(float);
+    static bool raised = false;
+    if (!raised) {
+        if (cudaFuncSetAttribute(attn_masked_decode_kernel<W, EXACT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 216 * 1024) != cudaSuccess)
+            return launch_status();
+        raised = true;
+    }
+    launch_kernel(attn_masked_decode_kernel<W, EXACT>, dim3(p.S, p.G, p.splits), dim3(nw * 32), smem, stream, p);
+    if (p.splits > 1) launch_kernel(attn_masked_merge_kernel, dim3(p.S, p.G, (p.H / p.G * p.dv + 127) / 128), dim3(128), 0, stream, p);
+    return launch_status();
+}
+
 }  // namespace cvb
 
 using namespace cvb;
@@ -525,7 +936,16 @@ extern "C" int cvb_masked_qkv_prep(void* q_out, const void* packed, int T, int s
     dim3 grid(static_cast<unsigned>(T), static_cast<unsigned>((tasks + kPrepWarps - 1) / kPrepWarps));
     const size_t smem = static_cast<size_t>(kPrepWarps) * dk * sizeof(float);
     if (smem > 48 * 1024 || grid.y > 65535) return CVB_E_SIZE;
+    const bool turns = rot > 0 && cos_t != nullptr;
+    const bool pairs = dk % 2 == 0 && dv % 2 == 0 && stride % 2 == 0 && dk <= 64 * kPrepPairs && (interleaved || !turns)
+                       && ((reinterpret_cast<uintptr_t>(packed) | reinterpret_cast<uintptr_t>(q_out) | reinterpret_cast<uintptr_t>(pages)
+                            | reinterpret_cast<uintptr_t>(vfirst_out) | reinterpret_cast<uintptr_t>(vfirst_in)) & 7) == 0;
 #define CALL(TY)                                                                                                          \
+    if (pairs)                                                                                                            \
+    launch_kernel(masked_qkv_prep_pairs_kernel<TY>, grid, dim3(kPrepWarps * 32), 0, stream, (TY*)q_out, (const TY*)packed, stride, q_w, \
+                  k_w, cos_t, sin_t, positions, slots, (TY*)pages, (TY*)vfirst_out, (const TY*)vfirst_in, lam, H, G, dk, dv, rot,    \
+                  planes, page_size, max_pos, eps, total_slots, err_flag);                                                \
+    else                                                                                                                  \
     launch_kernel(masked_qkv_prep_kernel<TY>, grid, dim3(kPrepWarps * 32), smem, stream, (TY*)q_out, (const TY*)packed, stride, q_w, \
                   k_w, cos_t, sin_t, positions, slots, (TY*)pages, (TY*)vfirst_out, (const TY*)vfirst_in, lam, H, G, dk, dv, rot,    \
                   interleaved, planes, page_size, max_pos, eps, total_slots, err_flag)
@@ -538,7 +958,7 @@ extern "C" int cvb_pool_entries(void* pages, const int* block_tables, int table_
                                 int T, int G, int ew, int pool, int page_size, int num_pages, int dtype, int* err_flag,
                                 cudaStream_t stream) {
     if (T == 0) return CVB_OK;
-    if (T < 0 || G <= 0 || ew <= 0 || pool <= 0 || page_size <= 0 || table_width <= 0 || num_pages <= 0 || G > 65535) return CVB_E_SIZE;
+    if (T < 0 || G <= 0 || ew <= 0 || ew > 512 || pool <= 0 || page_size <= 0 || table_width <= 0 || num_pages <= 0 || G > 65535) return CVB_E_SIZE;
 #define CALL(TY)                                                                                                          \
     launch_kernel(pool_entries_kernel<TY>, dim3(T, G), dim3(128), 0, stream, (TY*)pages, block_tables, table_width, seq_of_token,   \
                   positions, G, ew, pool, page_size, num_pages, err_flag)
@@ -580,7 +1000,8 @@ extern "C" int cvb_attn_masked_bf16(void* out, const void* q, const void* pages,
                                     const int* cu_seqlens, const int* positions, int S, int num_tiles, int H, int G, int dk, int dv,
                                     int page_size, int planes, int chunk, int window, int pool, float scale, float softcap,
                                     const float* r1, const float* r2, const float* sink, const void* gate, int gate_stride,
-                                    int num_pages, int* err_flag, cudaStream_t stream) {
+                                    int num_pages, int all_single, int splits, float* parts, int64_t parts_floats, int* err_flag,
+                                    cudaStream_t stream) {
     if (num_tiles == 0 || S == 0) return CVB_OK;
     if (S < 0 || num_tiles < 0 || page_size <= 0 || table_width <= 0 || num_pages <= 0) return CVB_E_SIZE;
     if (!cvb_attn_masked_supported(H, G, dk, dv)) return CVB_E_UNSUPPORTED;
@@ -602,10 +1023,20 @@ extern "C" int cvb_attn_masked_bf16(void* out, const void* q, const void* pages,
         if ((1 << sh) == page_size) p.page_shift = sh;
     p.mp = MaskParams{chunk, window, pool, scale, softcap};
     p.err = err_flag;
+    p.splits = 1; p.parts = nullptr;
+    const bool decode = all_single && H / G <= 16;        // every request brings one token: the kernel for decoded tokens
+    if (decode && splits > 1) {
+        if (splits > 64) return CVB_E_SIZE;
+        if (parts == nullptr || parts_floats < static_cast<int64_t>(S) * G * splits * 16 * (dv + 2)) return CVB_E_SCRATCH;
+        p.splits = splits; p.parts = parts;
+    }
     const int w = dk > dv ? dk : dv;
     const bool exact = dk == dv && (dk == 64 || dk == 128);
 #define CVB_MASKED_WIDTH(WW)                                                                                             \
-    if (w <= WW) return exact ? launch_attn_masked<WW, true>(p, num_tiles, stream) : launch_attn_masked<WW, false>(p, num_tiles, stream);
+    if (w <= WW) {                                                                                                       \
+        if (decode) return exact ? launch_attn_masked_decode<WW, true>(p, stream) : launch_attn_masked_decode<WW, false>(p, stream); \
+        return exact ? launch_attn_masked<WW, true>(p, num_tiles, stream) : launch_attn_masked<WW, false>(p, num_tiles, stream);     \
+    }
     CVB_MASKED_WIDTH(64)
     CVB_MASKED_WIDTH(128)
 #undef CVB_MASKED_WIDTH

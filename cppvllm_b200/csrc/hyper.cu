@@ -37,6 +37,85 @@ stream_embed_kernel(float* __restrict__ X, const T* __restrict__ table, const in
     }
 }
 
+__device__ __forceinline__ float4 load4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 load4(const __nv_bfloat16* p) {
+    const uint2 raw = *reinterpret_cast<const uint2*>(p);
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+    return make_float4(a.x, a.y, b.x, b.y);
+}
+__device__ __forceinline__ void store4(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+__device__ __forceinline__ void store4(__nv_bfloat16* p, float4 v) {
+    __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+    uint2 raw;
+    raw.x = *reinterpret_cast<uint32_t*>(&a);
+    raw.y = *reinterpret_cast<uint32_t*>(&b);
+    *reinterpret_cast<uint2*>(p) = raw;
+}
+
+// The same pass four elements at a time (D a multiple of 4) with the number of streams known to the compiler (1 to 4): 16-byte
+// loads and stores of the streams, 8- or 16-byte ones of the sublayer's output and of the normed row, the weights in
+// registers.  The order of every sum is that of the scalar form.
+template <typename T, int NS>
+__global__ void __launch_bounds__(kStreamThreads)
+stream_step_vec_kernel(float* __restrict__ X, const T* __restrict__ y, const float* __restrict__ mix, const float* __restrict__ wout,
+                       const float* __restrict__ win, const float* __restrict__ g, float eps, T* __restrict__ normed, int D) {
+    pdl_trigger();
+    extern __shared__ __align__(16) float smem[];
+    float* us = smem;                                   // [D]
+    float* scratch = smem + D;                          // [32]
+    float m_r[NS][NS], b_r[NS], a_r[NS];
+#pragma unroll
+    for (int s = 0; s < NS; ++s) {
+        b_r[s] = wout != nullptr ? wout[s] : 0.f;
+        a_r[s] = win != nullptr ? win[s] : 1.f;
+#pragma unroll
+        for (int to = 0; to < NS; ++to) m_r[s][to] = mix != nullptr ? mix[s * NS + to] : 0.f;
+    }
+    const float gw = g != nullptr ? g[0] : 1.f;
+    pdl_wait();
+    const int64_t t = blockIdx.x;
+    float* row = X + t * NS * D;
+    float ss = 0.f;
+    for (int d = threadIdx.x * 4; d < D; d += kStreamThreads * 4) {
+        float4 x[NS];
+#pragma unroll
+        for (int s = 0; s < NS; ++s) x[s] = load4(row + static_cast<int64_t>(s) * D + d);
+        if (y != nullptr) {
+            const float4 yv = load4(y + t * D + d);
+            float4 nx[NS];
+#pragma unroll
+            for (int to = 0; to < NS; ++to) {
+                float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                for (int s = 0; s < NS; ++s) {
+                    acc.x = fmaf(m_r[s][to], x[s].x, acc.x); acc.y = fmaf(m_r[s][to], x[s].y, acc.y);
+                    acc.z = fmaf(m_r[s][to], x[s].z, acc.z); acc.w = fmaf(m_r[s][to], x[s].w, acc.w);
+                }
+                nx[to] = make_float4(fmaf(b_r[to], yv.x, acc.x), fmaf(b_r[to], yv.y, acc.y), fmaf(b_r[to], yv.z, acc.z), fmaf(b_r[to], yv.w, acc.w));
+            }
+#pragma unroll
+            for (int s = 0; s < NS; ++s) { x[s] = nx[s]; store4(row + static_cast<int64_t>(s) * D + d, nx[s]); }
+        }
+        if (normed != nullptr) {
+            float4 u = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+            for (int s = 0; s < NS; ++s) {
+                u.x = fmaf(a_r[s], x[s].x, u.x); u.y = fmaf(a_r[s], x[s].y, u.y); u.z = fmaf(a_r[s], x[s].z, u.z); u.w = fmaf(a_r[s], x[s].w, u.w);
+            }
+            ss = fmaf(u.x, u.x, ss); ss = fmaf(u.y, u.y, ss); ss = fmaf(u.z, u.z, ss); ss = fmaf(u.w, u.w, ss);
+            store4(us + d, u);
+        }
+    }
+    if (normed == nullptr) return;
+    const float total = block_sum(ss, scratch);
+    const float inv = rsqrtf(total / static_cast<float>(D) + eps) * gw;
+    for (int d = threadIdx.x * 4; d < D; d += kStreamThreads * 4) {
+        const float4 u = load4(us + d);
+        store4(normed + t * D + d, make_float4(u.x * inv, u.y * inv, u.z * inv, u.w * inv));
+    }
+}
+
 template <typename T>
 __global__ void __launch_bounds__(kStreamThreads)
 stream_step_kernel(float* __restrict__ X, const T* __restrict__ y, const float* __restrict__ mix, const float* __restrict__ wout,
@@ -105,6 +184,7 @@ extern "C" int cvb_stream_embed(float* X, const void* table, const int* tokens, 
                                vocab, err_flag)
     CVB_DISPATCH_DTYPE(dtype, CALL);
 #undef CALL
+#undef VEC
     return launch_status();
 }
 
@@ -118,14 +198,28 @@ extern "C" int cvb_stream_step(float* X, const void* y, const float* mix, const 
     if (y == nullptr && normed == nullptr) return CVB_E_SHAPE;
     const size_t smem = (static_cast<size_t>(D) + 32) * sizeof(float);
     if (smem > 200 * 1024) return CVB_E_SIZE;
+    const bool wide = D % 4 == 0 && ((reinterpret_cast<uintptr_t>(X) | reinterpret_cast<uintptr_t>(y) | reinterpret_cast<uintptr_t>(normed)) & 15) == 0;
+#define VEC(TY, NS)                                                                                                       \
+    do {                                                                                                                  \
+        if (smem > 48 * 1024)                                                                                             \
+            cudaFuncSetAttribute(stream_step_vec_kernel<TY, NS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+        launch_kernel(stream_step_vec_kernel<TY, NS>, dim3(T), dim3(kStreamThreads), smem, stream, X, (const TY*)y, mix, wout, win, g, \
+                      eps, (TY*)normed, D);                                                                               \
+    } while (0)
 #define CALL(TY)                                                                                                          \
     do {                                                                                                                  \
         if (smem > 48 * 1024)                                                                                             \
             cudaFuncSetAttribute(stream_step_kernel<TY>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);         \
+        if (wide && S == 1) { VEC(TY, 1); }                                                                               \
+        else if (wide && S == 2) { VEC(TY, 2); }                                                                          \
+        else if (wide && S == 3) { VEC(TY, 3); }                                                                          \
+        else if (wide && S == 4) { VEC(TY, 4); }                                                                          \
+        else                                                                                                              \
         launch_kernel(stream_step_kernel<TY>, dim3(T), dim3(kStreamThreads), smem, stream, X, (const TY*)y, mix, wout, win, g, eps, \
                       (TY*)normed, S, D);                                                                                 \
     } while (0)
     CVB_DISPATCH_DTYPE(dtype, CALL);
 #undef CALL
+#undef VEC
     return launch_status();
 }

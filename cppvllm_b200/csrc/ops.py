@@ -1103,9 +1103,12 @@ def attn_masked_bf16(out: torch.Tensor, q: torch.Tensor, pages: torch.Tensor, bl
                      positions: torch.Tensor, num_seqs: int, num_tiles: int, num_heads: int, num_kv_heads: int, dim: int, vdim: int,
                      page_size: int, scale: float, planes: int = 1, chunk: int = 0, window: int = 0, pool: int = 0,
                      softcap: float = 0.0, r1: Optional[torch.Tensor] = None, r2: Optional[torch.Tensor] = None,
-                     sink: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None) -> torch.Tensor:
+                     sink: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None, all_single: bool = False,
+                     splits: int = 1, scratch: Optional[torch.Tensor] = None) -> torch.Tensor:
     """The tensor-core form of attn_masked_general for prompt portions and decoded tokens alike; `num_tiles` as
-    attn_keys_tiles gives it (blocks of 64 // group tokens of one request)."""
+    attn_keys_tiles gives it (blocks of 64 // group tokens of one request).  `all_single`: every request brings exactly one
+    token (the form for decoded tokens, up to 16 query heads per kv head); with `splits` > 1 that many blocks share a
+    (request, kv head), through `scratch` (float32, attn_keys_scratch_floats with vdim as the head size) and a merge kernel."""
     _cuda(out, q, pages, block_tables, cu_seqlens, positions, r1, r2, sink, gate)
     _contig(out, q, pages, block_tables, cu_seqlens, positions, r1, r2, sink)
     H = num_heads
@@ -1119,11 +1122,15 @@ def attn_masked_bf16(out: torch.Tensor, q: torch.Tensor, pages: torch.Tensor, bl
     if gate is not None and (gate.dtype != torch.bfloat16 or gate.shape[1] != H or gate.stride(1) != 1):
         raise KernelError("attn_masked_bf16: gate bf16 [T, H]")
     num_pages = pages.numel() // (planes * num_kv_heads * page_size * (dim + vdim))
+    if splits > 1 and (scratch is None or scratch.dtype != torch.float32 or not scratch.is_cuda or not scratch.is_contiguous()):
+        raise KernelError("attn_masked_bf16: splits need a contiguous float32 CUDA scratch")
     _check(_attn_masked_lib().cvb_attn_masked_bf16(
         _ptr(out), _ptr(q), _ptr(pages), _ptr(block_tables), c_int(block_tables.shape[1]), _ptr(cu_seqlens), _ptr(positions),
         c_int(num_seqs), c_int(num_tiles), c_int(H), c_int(num_kv_heads), c_int(dim), c_int(vdim), c_int(page_size), c_int(planes),
         c_int(chunk), c_int(window), c_int(pool), c_float(scale), c_float(softcap), _ptr(r1), _ptr(r2), _ptr(sink), _ptr(gate),
-        c_int(gate.stride(0) if gate is not None else 0), c_int(num_pages), _ptr(error_flag(q.device)), _stream()), "attn_masked_bf16")
+        c_int(gate.stride(0) if gate is not None else 0), c_int(num_pages), c_int(1 if all_single else 0), c_int(splits), _ptr(scratch),
+        c_int64(scratch.numel() if scratch is not None else 0), _ptr(error_flag(q.device)), _stream()), "attn_masked_bf16",
+        kernels=2 if all_single and splits > 1 else 1)
     return out
 
 

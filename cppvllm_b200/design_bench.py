@@ -30,6 +30,15 @@ squared-relu experts of half the inner size, 2 per token, with a shared expert. 
 existing model: a float32 stream, attention over cache entries, routed experts) and Qwen3; its kernels beside the like kernels of
 Givirax (attention, experts), Dugulorn (the delta rule, the norm behind a sublayer) and Qwen3 (the projection's epilogue, the
 activation).
+    python bench.py --design rumurax
+
+The Rumurax model of a size has the same width, heads and head size; two residual streams; its layers repeat the pattern
+[attention with a rotation behind a window of 1,024 tokens and pooled blocks of 64, chunked attention (chunks of 1,024, capped
+scores, distance term, sink, gate per head), attention over a latent of 96 + 32 elements, chunked attention], every layer with 8
+gated experts, 2 per token, of half the inner size, whose logistic scores multiply their inputs, and a shared expert of the same
+size.  Whole models stand beside Givirax (the closest existing model: a float32 stream, attention over cache entries behind a
+window, routed gated experts) and Qwen3; its kernels beside the like kernels of Lorulix (attention over entries of a key and its
+value), Givirax (the stream update, the router, the experts), Qwen3 (the projection's epilogue) and Dugulorn (the gate).
 """
 from __future__ import annotations
 
@@ -105,6 +114,23 @@ def lorulix_config(s, max_positions):
             layers.append({"type": "delta", "mixer": delta, "mlp": moe if k == 1 else dense})
     return {"architecture": "Lorulix", "vocab": s["vocab"], "width": s["width"], "max_positions": max_positions,
             "norm": {"eps": 1e-5}, "canon": {"taps": 4}, "layers": layers}
+
+
+RX_WINDOW, RX_POOL, RX_CHUNK = 1024, 64, 1024
+
+
+def rumurax_config(s, max_positions):
+    H, KV, hd, I = s["heads"], s["kv_heads"], s["dim"], s["ff"]
+    windowed = {"type": "attention_2", "mixer": {"dim": hd, "heads": H, "kv_heads": KV, "vdim": hd, "scale": 1.0 / math.sqrt(hd),
+                                                 "mask": {"size": RX_WINDOW, "pool": RX_POOL}, "rot": {"dims": hd, "base": 1.0e6}, "v_mix": True}}
+    chunked = {"type": "attention", "mixer": {"dim": hd, "heads": H, "kv_heads": KV, "vdim": hd, "scale": 1.0 / math.sqrt(hd),
+                                              "mask": {"size": RX_CHUNK}, "softcap": 30.0, "v_mix": True}}
+    latent = {"type": "latent_attention", "mixer": {"heads": H, "dim": hd, "rot_dim": 32, "vdim": hd, "kv_rank": 96,
+                                                    "scale": 1.0 / math.sqrt(hd + 32), "rot": {"dims": 32, "base": 1.0e6}}}
+    moe = {"kind": "moe", "expert": {"ff": I // 2}, "router": {"experts": EXPERTS, "top": TOP}, "shared": {"ff": I // 2}}
+    pattern = [windowed, chunked, latent, chunked]
+    return {"architecture": "Rumurax", "vocab": s["vocab"], "width": s["width"], "streams": 2, "norm": {"eps": 1e-5},
+            "layers": [dict(pattern[i % 4], mlp=moe) for i in range(s["layers"])]}
 
 
 def qwen3_config(s, max_positions):
@@ -649,9 +675,157 @@ def lorulix_kernel_pairs(s, pk):
     return out
 
 
+def rumurax_kernel_pairs(s, pk):
+    """The kernels that the Rumurax parts brought, each beside the like kernel of an existing model at the same sizes (`like`
+    names it)."""
+    from .csrc import ops
+    from .parts.base import Workspace
+    d = torch.device("cuda:0")
+    g = torch.Generator(device="cuda").manual_seed(0)
+    bf, f32, i32 = torch.bfloat16, torch.float32, torch.int32
+    D, H, KV, hd, I = s["width"], s["heads"], s["kv_heads"], s["dim"], s["ff"]
+    F = I // 2
+    page, out = 32, {}
+    hbm, flop = pk["hbm_gbs"] * 1e9, pk["bf16_tflops"] * 1e12
+
+    def rnd(*shape, scale=1.0, dtype=bf):
+        return (torch.randn(*shape, generator=g, device=d, dtype=f32) * scale).to(dtype)
+
+    def pair(name, new_us, new_work, like_us, like_work, unit, like, note=None):
+        peak = hbm if unit == "bytes" else flop
+        fn, fl = new_work / (new_us * 1e-6) / peak, like_work / (like_us * 1e-6) / peak
+        out[name] = {"new_us": round(new_us, 2), "new_frac": round(fn, 4), "like_us": round(like_us, 2), "like_frac": round(fl, 4),
+                     "gap": round(fl / fn, 2), "roofline": "copy bandwidth" if unit == "bytes" else "bf16 peak", "like": like}
+        if note:
+            out[name]["note"] = note
+
+    # -- attention of a prompt of 2,048 tokens ---------------------------------------------------------------------------
+    T = 2048
+    n_pages = T // page
+    tables = torch.arange(n_pages, dtype=i32, device=d).view(1, n_pages)
+    cu = torch.tensor([0, T], dtype=i32, device=d)
+    pos = torch.arange(T, dtype=i32, device=d)
+    scale = 1 / math.sqrt(hd)
+    q = rnd(T, H * hd)
+    att = torch.empty(T, H * hd, dtype=bf, device=d)
+    tiles = ops.attn_keys_tiles([T], H, KV)
+    r1, r2, sink = torch.rand(H, device=d), torch.rand(H, device=d), torch.randn(H, device=d)
+    gate = rnd(T, H)
+    ent1 = rnd(n_pages + 1, KV, page, 2 * hd)
+    ent2 = rnd(n_pages + 1, 2, KV, page, 2 * hd)
+    bias = rnd(H, BIAS_FAR + 1, dtype=f32)
+    like = _us(lambda i: ops.attn_bias_bf16(att, q, ent1, tables, cu, pos, 1, tiles, H, KV, hd, hd, page, scale, bias))
+    like_flops = 4.0 * H * hd * T * (T + 1) / 2
+    seen = sum(p % RX_CHUNK + 1 for p in range(T))
+    new = _us(lambda i: ops.attn_masked_bf16(att, q, ent1, tables, cu, pos, 1, tiles, H, KV, hd, hd, page, scale, chunk=RX_CHUNK, softcap=30.0,
+                                             r1=r1, r2=r2, sink=sink, gate=gate))
+    pair("attention_chunked_prefill_2048", new, 4.0 * H * hd * seen, like, like_flops, "flops", "Lorulix attn_bias_kernel, all earlier keys",
+         note="chunks of 1,024: half the keys of the like kernel; cap, distance term, sink and gate on the score fragments")
+    seen = sum(min(p + 1, RX_WINDOW) + max(0, (p - RX_WINDOW + 1) // RX_POOL) for p in range(T))
+    new = _us(lambda i: ops.attn_masked_bf16(att, q, ent2, tables, cu, pos, 1, tiles, H, KV, hd, hd, page, scale, planes=2, window=RX_WINDOW,
+                                             pool=RX_POOL))
+    pair("attention_windowed_prefill_2048", new, 4.0 * H * hd * seen, like, like_flops, "flops", "Lorulix attn_bias_kernel, all earlier keys",
+         note="a window of 1,024 and the pooled blocks before it")
+    kv_pages = rnd(n_pages + 1, 2, KV, page, hd)
+    tiles_tc = ops.prefill_tiles_tcgen05([T], H, KV)
+    like_tc = _us(lambda i: ops.attn_prefill_tcgen05(att, q, kv_pages, tables, cu, pos, 1, tiles_tc, H, KV, hd, page, scale))
+    out["attention_chunked_prefill_2048"]["qwen3_tcgen05_us"] = round(like_tc, 2)
+    out["attention_chunked_prefill_2048"]["qwen3_tcgen05_frac"] = round(like_flops / (like_tc * 1e-6) / flop, 4)
+
+    # -- attention of decoded tokens: batch 8 at 4,096 tokens ---------------------------------------------------------------
+    B, ctx = 8, 4096
+    pps = ctx // page
+    copies = 4
+    tabs = [torch.randperm(B * pps, generator=g, device=d).to(i32).view(B, pps).contiguous() for _ in range(copies)]
+    e1_big = [rnd(B * pps + 1, KV, page, 2 * hd) for _ in range(copies)]
+    e2_big = [rnd(B * pps + 1, 2, KV, page, 2 * hd) for _ in range(copies)]
+    cu_b = torch.arange(0, B + 1, dtype=i32, device=d)
+    pos_b = torch.full((B,), ctx - 1, dtype=i32, device=d)
+    q_b, gate_b = rnd(B, H * hd), rnd(B, H)
+    att_b = torch.empty(B, H * hd, dtype=bf, device=d)
+    z = ops.attn_keys_decode_splits(B, KV, ctx)
+    parts = torch.empty(max(1, ops.attn_keys_scratch_floats(B, KV, hd, z)), dtype=f32, device=d)
+    like = _us(lambda i: ops.attn_bias_bf16(att_b, q_b, e1_big[i % copies], tabs[i % copies], cu_b, pos_b, B, B, H, KV, hd, hd, page, scale,
+                                            bias, all_single=True, splits=z, scratch=parts))
+    like_bytes = B * ctx * KV * hd * 4.0
+    zm = ops.attn_keys_decode_splits(B, KV, RX_CHUNK)
+    new = _us(lambda i: ops.attn_masked_bf16(att_b, q_b, e1_big[i % copies], tabs[i % copies], cu_b, pos_b, B, B, H, KV, hd, hd, page, scale,
+                                             chunk=RX_CHUNK, softcap=30.0, r1=r1, r2=r2, sink=sink, gate=gate_b, all_single=True, splits=zm,
+                                             scratch=parts))
+    pair("attention_chunked_decode_b8_ctx_4096", new, B * RX_CHUNK * KV * hd * 4.0, like, like_bytes, "bytes",
+         "Lorulix attn_bias_decode_kernel, 4,096 keys", note="the last token of a chunk: 1,024 keys")
+    nb = (ctx - RX_WINDOW) // RX_POOL
+    new = _us(lambda i: ops.attn_masked_bf16(att_b, q_b, e2_big[i % copies], tabs[i % copies], cu_b, pos_b, B, B, H, KV, hd, hd, page, scale,
+                                             planes=2, window=RX_WINDOW, pool=RX_POOL, all_single=True, splits=zm, scratch=parts))
+    pair("attention_windowed_decode_b8_ctx_4096", new, B * (RX_WINDOW + nb) * KV * hd * 4.0, like, like_bytes, "bytes",
+         "Lorulix attn_bias_decode_kernel, 4,096 keys", note="1,024 keys and 48 pooled blocks")
+    del e1_big, e2_big
+
+    # -- the projection's epilogue, 2,048 tokens: per-head norms, rotation, value mixing, cache write, pooled blocks -----------
+    packed = rnd(T, (H + 2 * KV) * hd)
+    q_out = torch.empty(T, H * hd, dtype=bf, device=d)
+    w1 = torch.ones(hd, device=d)
+    slots_t = torch.arange(T, dtype=i32, device=d)
+    cos, sin = torch.rand(T, hd // 2, generator=g, device=d), torch.rand(T, hd // 2, generator=g, device=d)
+    vf, lam = rnd(T, KV * hd), torch.tensor([0.3], device=d)
+    seq_of = torch.zeros(T, dtype=i32, device=d)
+    new = _us(lambda i: ops.masked_qkv_prep(q_out, packed, H, KV, hd, hd, 1e-5, q_weight=w1, k_weight=w1, cos=cos, sin=sin, rot=hd, positions=pos,
+                                            pages=ent2, slots=slots_t, page_size=page, planes=2, v_first_in=vf, lam=lam))
+    like = _us(lambda i: ops.qk_norm_rope_kv(q_out, packed, w1, w1, cos, sin, pos, slots_t, kv_pages, H, KV, hd, page, 1e-6))
+    moved = T * (H + 2 * KV) * hd * 4.0
+    pair("projection_epilogue_2048_tokens", new, moved + T * KV * hd * 2.0, like, moved, "bytes", "Qwen3 qk_norm_rope_kv", note="also mixes the values")
+    new = _us(lambda i: ops.pool_entries(ent2, tables, seq_of, pos, T, KV, 2 * hd, RX_POOL, page))
+    out["pooled_blocks_2048_tokens"] = {"new_us": round(new, 2), "new_frac": round(T * KV * 2 * hd * 2.0 * (1 + 1 / RX_POOL) / (new * 1e-6) / hbm, 4),
+                                        "roofline": "copy bandwidth", "note": "no like kernel in an existing model"}
+
+    # -- the streams: a sublayer's write and the next one's read and norm, beside the float32 stream update --------------------
+    S = 2
+    X = torch.randn(T, S * D, generator=g, device=d)
+    yy, nxt = rnd(T, D), torch.empty(T, D, dtype=bf, device=d)
+    mix, a, b, gw = torch.eye(S, device=d).contiguous(), torch.ones(S, device=d), torch.ones(S, device=d), torch.ones(1, device=d)
+    new = _us(lambda i: ops.stream_step(X, S, write=(yy, mix, b), read=(a, gw), eps=1e-5, out=nxt))
+    h32, w = torch.randn(T, D, generator=g, device=d), torch.ones(D, device=d)
+    like = _us(lambda i: ops.resid_update(h32, (yy,), norm_weight=w, eps=1e-5, out=nxt))
+    pair("stream_step_2048_tokens", new, T * D * (S * 8 + 4.0), like, T * D * (8 + 4.0), "bytes", "Givirax resid_update", note="two streams")
+
+    # -- feed-forwards ---------------------------------------------------------------------------------------------------------
+    x = rnd(T, D)
+    w_router = torch.randn(EXPERTS, D, generator=g, device=d)
+    ids, wts = torch.empty(T, TOP, dtype=i32, device=d), torch.empty(T, TOP, dtype=f32, device=d)
+    new = _us(lambda i: ops.route_topk(ids, wts, x, w_router, None, logistic=True))
+    b_r8 = torch.zeros(EXPERTS, device=d)
+    ids2, wts2 = torch.empty(T, TOP, dtype=i32, device=d), torch.empty(T, TOP, dtype=f32, device=d)
+    like = _us(lambda i: ops.route_topk(ids2, wts2, x, w_router, b_r8))
+    pair("router_2048_tokens", new, T * D * 2.0, like, T * D * 2.0, "bytes", "Givirax route_topk")
+    ws = Workspace(d, T)
+    w_gu, w_dn = rnd(EXPERTS, 2 * F, D, scale=0.02), rnd(EXPERTS, D, F, scale=0.02)
+    y = torch.empty(T, D, dtype=bf, device=d)
+    new = _us(lambda i: ops.routed_experts(y, x, ids, wts, w_gu, w_dn, workspace=ws, weight_on_input=True))
+    like = _us(lambda i: ops.routed_experts(y, x, ids2, wts2, w_gu, w_dn, workspace=ws))
+    work = 2.0 * T * TOP * 3 * D * F
+    pair("experts_2048_tokens", new, work, like, work, "flops", "Givirax gated experts", note="the weight scales the rows on their way into the grouped product")
+    ws8 = Workspace(d, 8)
+    copies = max(2, int(300e6 // (w_gu.numel() * 2 + w_dn.numel() * 2)) + 1)
+    gus = [w_gu] + [rnd(EXPERTS, 2 * F, D, scale=0.02) for _ in range(copies - 1)]
+    dns = [w_dn] + [rnd(EXPERTS, D, F, scale=0.02) for _ in range(copies - 1)]
+    x8, y8 = x[:8].contiguous(), torch.empty(8, D, dtype=bf, device=d)
+    ids8, wts8, ids28, wts28 = ids[:8].contiguous(), wts[:8].contiguous(), ids2[:8].contiguous(), wts2[:8].contiguous()
+    new = _us(lambda i: ops.routed_experts(y8, x8, ids8, wts8, gus[i % copies], dns[i % copies], workspace=ws8, weight_on_input=True))
+    like = _us(lambda i: ops.routed_experts(y8, x8, ids28, wts28, gus[i % copies], dns[i % copies], workspace=ws8))
+    used, used2 = len(set(ids8.flatten().tolist())), len(set(ids28.flatten().tolist()))
+    pair("experts_8_decoded_tokens", new, used * 3.0 * D * F * 2, like, used2 * 3.0 * D * F * 2, "bytes", "Givirax gated experts")
+
+    # -- the gate per element behind latent attention, beside the gate per head ---------------------------------------------------
+    o_h, g_el, g_hd = rnd(H, T, hd), rnd(T, H * hd), rnd(T, H)
+    new = _us(lambda i: ops.head_gate(att, o_h, g_el, H, hd, per_element=True))
+    like = _us(lambda i: ops.head_gate(att, o_h, g_hd, H, hd))
+    pair("gate_2048_tokens", new, T * H * hd * 6.0, like, T * H * hd * 4.0, "bytes", "Dugulorn head_gate, one number per head")
+    return out
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="design_bench", description=__doc__.split("\n\n")[0])
-    ap.add_argument("--design", default="givirax", choices=["givirax", "dugulorn", "lorulix"])
+    ap.add_argument("--design", default="givirax", choices=["givirax", "dugulorn", "lorulix", "rumurax"])
     ap.add_argument("--sizes", default="small,large")
     ap.add_argument("--steps", type=int, default=48)
     ap.add_argument("--no-kernels", action="store_true", help="whole models only")
@@ -668,19 +842,22 @@ def main(argv=None) -> int:
         result.update(window=WINDOW, keep_first=KEEP, experts=EXPERTS, top=TOP)
     if a.design == "lorulix":
         result.update(closest="Givirax", bias_rows=BIAS_ROWS, bias_far=BIAS_FAR, experts=EXPERTS, top=TOP)
+    if a.design == "rumurax":
+        result.update(closest="Givirax", window=RX_WINDOW, pool=RX_POOL, chunk=RX_CHUNK, streams=2, experts=EXPERTS, top=TOP)
     for name in a.sizes.split(","):
         s = SIZES[name]
         entry = {"shape": s}
         if not a.no_models:
             t0 = time.time()
-            design_config = {"givirax": givirax_config, "dugulorn": dugulorn_config, "lorulix": lorulix_config}[a.design]
+            design_config = {"givirax": givirax_config, "dugulorn": dugulorn_config, "lorulix": lorulix_config, "rumurax": rumurax_config}[a.design]
             entry[a.design] = model_points(design_config(s, 4160), 2048, 8, 4096, a.steps)
-            if a.design == "lorulix":
+            if a.design in ("lorulix", "rumurax"):
                 entry["givirax"] = model_points(givirax_config(s, 4160), 2048, 8, 4096, a.steps)
             entry["qwen3"] = model_points(qwen3_config(s, 4160), 2048, 8, 4096, a.steps)
             entry["seconds"] = round(time.time() - t0, 1)
         if not a.no_kernels:
-            entry["kernels"] = {"givirax": kernel_pairs, "dugulorn": dugulorn_kernel_pairs, "lorulix": lorulix_kernel_pairs}[a.design](s, pk)
+            entry["kernels"] = {"givirax": kernel_pairs, "dugulorn": dugulorn_kernel_pairs, "lorulix": lorulix_kernel_pairs,
+                                "rumurax": rumurax_kernel_pairs}[a.design](s, pk)
         result["sizes"][name] = entry
     print(json.dumps(result))
     return 0

@@ -130,10 +130,23 @@ class MaskedAttention(Mixer):
         H, G, dk, dv = self.num_heads, self.num_kv_heads, self.dim, self.vdim
         if not self.force_general and ops.attn_masked_supported(q.dtype, H, G, dk, dv):
             q_lens = ctx.q_lens if ctx.q_lens is not None else [1] * ctx.num_seqs
+            single = ctx.all_decode and ctx.num_tokens == ctx.num_seqs and H // G <= 16
+            splits, scratch = 1, None
+            if single:
+                # what a decoded token can see at most: its chunk, or its window and the pooled blocks before it
+                seen = ctx.max_kv_len
+                if self.chunk:
+                    seen = min(seen, self.chunk)
+                if self.window:
+                    seen = min(seen, self.window + (ctx.max_kv_len // self.pool if self.pool else 0))
+                splits = ops.attn_keys_decode_splits(ctx.num_seqs, G, seen)
+                if splits > 1:
+                    most = ops.attn_keys_scratch_floats(self.rt.workspace.max_seqs, G, dv, 8)
+                    scratch = self.rt.workspace.flat(f"attn_masked_parts_{G}_{dv}", most, torch.float32)
             ops.attn_masked_bf16(att, q, cache.pages, g.block_tables, ctx.cu_seqlens, ctx.positions, ctx.num_seqs,
                                  ops.attn_keys_tiles(q_lens, H, G), H, G, dk, dv, g.page_size, self.scale, planes=self.planes,
                                  chunk=self.chunk, window=self.window, pool=self.pool, softcap=self.softcap, r1=self.r1, r2=self.r2,
-                                 sink=self.sinks, gate=gate)
+                                 sink=self.sinks, gate=gate, all_single=single, splits=splits, scratch=scratch)
             return
         ops.attn_masked_general(att, q, cache.pages, g.block_tables, ctx.seq_of_token, ctx.positions, ctx.num_tokens, H, G, dk, dv,
                                 g.page_size, self.scale, planes=self.planes, chunk=self.chunk, window=self.window, pool=self.pool,

@@ -228,10 +228,11 @@ def routed_experts(h, w, p, f, rnd=identity, margins=None):
         ordered = torch.sort(z, dim=1, descending=True).values
         margins.append(ordered[:, top - 1] - ordered[:, top] if top < E else torch.full((T,), math.inf, dtype=F))
     y = torch.zeros_like(h)
-    for t in range(T):
-        for c in range(top):
-            e = int(best.indices[t, c])
-            y[t] += expert(rnd(s[t, e] * h[t:t + 1]), w, f"{p}e{e}.", rnd)[0]
+    for c in range(top):                                                       # the tokens whose c-th choice is expert e, together
+        for e in range(E):
+            rows = (best.indices[:, c] == e).nonzero().flatten()
+            if len(rows):
+                y[rows] += expert(rnd(s[rows, e:e + 1] * h[rows]), w, f"{p}e{e}.", rnd)
     if f.get("shared") is not None:
         y = y + expert(h, w, p + "shared.", rnd)
     return y

@@ -174,6 +174,7 @@ def random_tokens(vocab, n, seed):
 
 
 _CLEAR = {}
+_REFERENCE = {}
 
 
 def clear_tokens(model_dir, n, seed, margin=0.3):
@@ -224,7 +225,10 @@ def reference(model_dir, tokens, layer_outputs=None):
     """Logits of one whole sequence from the plain implementation, which reads the folder with its own readers."""
     import plain_rumurax as plain
     if layer_outputs is None:
-        return plain.forward(model_dir, tokens)
+        key = (model_dir, tuple(tokens))
+        if key not in _REFERENCE:
+            _REFERENCE[key] = plain.forward(model_dir, tokens)
+        return _REFERENCE[key]
     logits, layers = plain.forward(model_dir, tokens, return_layers=True)
     layer_outputs.extend(layers)
     return logits

@@ -74,7 +74,7 @@ def test_whole_tail_and_portions_match_the_plain_implementation(rx_dirs, name, d
     assert all(runner.cache.num_free_pages(g) == 128 // rm.page_size(name) for g in range(len(runner.group_specs)))
 
 
-@pytest.mark.parametrize("seed,dtype", [(s, "float32") for s in range(10)] + [(s, "bfloat16") for s in range(20, 26)])
+@pytest.mark.parametrize("seed,dtype", [(s, "float32") for s in range(6)] + [(s, "bfloat16") for s in range(20, 24)])
 def test_configurations_drawn_at_random(tmp_path, seed, dtype):
     """Layers of the three kinds in any order and size (tests/rumurax_models.py: random_config): a whole prompt, a tail decoded
     token by token, portions down to two tokens and three unequal requests in one batch.  In float32 nothing but the order of

@@ -292,3 +292,56 @@ def test_gate_per_element(dtype):
     ops.head_gate(out, o, packed[:, 7:], H, dv, per_element=True)
     want = o.double().cpu().permute(1, 0, 2).reshape(T, H * dv) * torch.sigmoid(packed[:, 7:].double().cpu())
     assert float((out.double().cpu() - want).abs().max()) < TOL[dtype] * float(want.abs().max())
+
+
+@pytest.mark.parametrize("splits", [1, 2, 4])
+@pytest.mark.parametrize("kind", ["chunked", "windowed", "causal"])
+def test_decoded_tokens_of_several_requests(kind, splits):
+    """The form for steps of one token per request (tiles shared out among warps and blocks, parts merged, the sink and the gate
+    joined once at the merge) against the general kernel, over requests of unequal lengths in shuffled pages."""
+    from cppvllm_b200.csrc import ops
+    g = torch.Generator().manual_seed(11)
+    H, G, dk, dv, page = 8, 2, 48, 64, 16
+    chunk, window, pool, cap = (64, 0, 0, 20.0) if kind == "chunked" else ((0, 136, 12, 0.0) if kind == "windowed" else (0, 0, 0, 0.0))
+    planes = 2 if pool else 1
+    lens = [1, 17, 64, 65, 300, 777, 128, 137]
+    B, E = len(lens), dk + dv
+    per = [(n + page - 1) // page for n in lens]
+    total = sum(per) + 2
+    order = torch.randperm(total, generator=g)
+    shape = (total, planes, G, page, E) if planes == 2 else (total, G, page, E)
+    pages = torch.randn(shape, generator=g).to(torch.bfloat16)
+    table = torch.full((B, max(per)), -1, dtype=torch.int32)
+    at = 0
+    owned = torch.zeros(total, dtype=torch.bool)
+    for b, n in enumerate(per):
+        table[b, :n] = order[at:at + n].to(torch.int32)
+        owned[order[at:at + n]] = True
+        last = lens[b] % page
+        if last:                                           # NaN behind the request's last token
+            pg = int(order[at + n - 1])
+            if planes == 2:
+                pages[pg, 0, :, last:] = float("nan")
+            else:
+                pages[pg, :, last:] = float("nan")
+        at += n
+    pages[~owned] = float("nan")
+    pages, table = pages.to(dev()), table.to(dev())
+    q = torch.randn(B, H * dk, generator=g).to(torch.bfloat16).to(dev())
+    pos = torch.tensor([n - 1 for n in lens], dtype=torch.int32, device=dev())
+    cu = torch.arange(B + 1, dtype=torch.int32, device=dev())
+    seq = torch.arange(B, dtype=torch.int32, device=dev())
+    r1 = r2 = sk = gt = None
+    if kind == "chunked":
+        r1, r2 = (0.5 + torch.rand(H, generator=g)).to(dev()), (0.2 + torch.rand(H, generator=g)).to(dev())
+        sk = (2.0 * torch.randn(H, generator=g)).to(dev())
+        gt = torch.randn(B, H, generator=g).to(torch.bfloat16).to(dev())
+    kw = dict(planes=planes, chunk=chunk, window=window, pool=pool, softcap=cap, r1=r1, r2=r2, sink=sk, gate=gt)
+    want = torch.empty(B, H * dv, dtype=torch.bfloat16, device=dev())
+    ops.attn_masked_general(want, q, pages, table, seq, pos, B, H, G, dk, dv, page, 0.2, **kw)
+    got = torch.empty_like(want)
+    scratch = torch.empty(ops.attn_keys_scratch_floats(B, G, dv, splits), dtype=torch.float32, device=dev())
+    ops.attn_masked_bf16(got, q, pages, table, cu, pos, B, B, H, G, dk, dv, page, 0.2, all_single=True, splits=splits, scratch=scratch, **kw)
+    ops.check_device_errors(dev())
+    assert torch.isfinite(got.float()).all()
+    assert float((got.float() - want.float()).abs().max()) < 2e-2 * max(1.0, float(want.float().abs().max()))
