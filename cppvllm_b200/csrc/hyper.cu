@@ -4,6 +4,7 @@
 //   X [T, S, D] float: the S streams of every token.  A sublayer f with numbers a[S] (read), M[S, S] (from, to), b[S] (write)
 //   and a norm with ONE weight g:
 //       u = sum_s a_s x_s;   h = T( u / sqrt(mean(u^2) + eps) * g );   y = f(h);   x_t <- sum_s M[s, t] x_s + b_t y
+//   (y may arrive as two addends that are summed in float: the routed experts' output and the shared expert's)
 //   stream_embed : x_s = table[token] for every s
 //   stream_step  : the write of one sublayer (optional) and the read and norm for the next (optional) in one pass: a block
 //                  holds a token's row, forms the new streams from the old ones element by element (all S values of an
@@ -58,7 +59,7 @@ __device__ __forceinline__ void store4(__nv_bfloat16* p, float4 v) {
 // registers.  The order of every sum is that of the scalar form.
 template <typename T, int NS>
 __global__ void __launch_bounds__(kStreamThreads)
-stream_step_vec_kernel(float* __restrict__ X, const T* __restrict__ y, const float* __restrict__ mix, const float* __restrict__ wout,
+stream_step_vec_kernel(float* __restrict__ X, const T* __restrict__ y, const T* __restrict__ y2, const float* __restrict__ mix, const float* __restrict__ wout,
                        const float* __restrict__ win, const float* __restrict__ g, float eps, T* __restrict__ normed, int D) {
     pdl_trigger();
     extern __shared__ __align__(16) float smem[];
@@ -82,7 +83,8 @@ stream_step_vec_kernel(float* __restrict__ X, const T* __restrict__ y, const flo
 #pragma unroll
         for (int s = 0; s < NS; ++s) x[s] = load4(row + static_cast<int64_t>(s) * D + d);
         if (y != nullptr) {
-            const float4 yv = load4(y + t * D + d);
+            float4 yv = load4(y + t * D + d);
+            if (y2 != nullptr) { const float4 z = load4(y2 + t * D + d); yv.x += z.x; yv.y += z.y; yv.z += z.z; yv.w += z.w; }
             float4 nx[NS];
 #pragma unroll
             for (int to = 0; to < NS; ++to) {
@@ -118,7 +120,7 @@ stream_step_vec_kernel(float* __restrict__ X, const T* __restrict__ y, const flo
 
 template <typename T>
 __global__ void __launch_bounds__(kStreamThreads)
-stream_step_kernel(float* __restrict__ X, const T* __restrict__ y, const float* __restrict__ mix, const float* __restrict__ wout,
+stream_step_kernel(float* __restrict__ X, const T* __restrict__ y, const T* __restrict__ y2, const float* __restrict__ mix, const float* __restrict__ wout,
                    const float* __restrict__ win, const float* __restrict__ g, float eps, T* __restrict__ normed, int S, int D) {
     pdl_trigger();
     extern __shared__ float smem[];
@@ -142,7 +144,7 @@ stream_step_kernel(float* __restrict__ X, const T* __restrict__ y, const float* 
         for (int s = 0; s < kMaxStreams; ++s)
             if (s < S) x[s] = row[static_cast<int64_t>(s) * D + d];
         if (y != nullptr) {
-            const float yv = to_float(y[t * D + d]);
+            const float yv = to_float(y[t * D + d]) + (y2 != nullptr ? to_float(y2[t * D + d]) : 0.f);
             float nx[kMaxStreams];
 #pragma unroll
             for (int to = 0; to < kMaxStreams; ++to) {
@@ -188,22 +190,22 @@ extern "C" int cvb_stream_embed(float* X, const void* table, const int* tokens, 
     return launch_status();
 }
 
-// y, mix, wout: the write (all or none).  normed: the read and norm (win and g optional: ones).
-extern "C" int cvb_stream_step(float* X, const void* y, const float* mix, const float* wout, const float* win, const float* g,
+// y, mix, wout: the write (all or none); y2: a second output added to y in float (a shared expert beside the routed ones).  normed: the read and norm (win and g optional: ones).
+extern "C" int cvb_stream_step(float* X, const void* y, const void* y2, const float* mix, const float* wout, const float* win, const float* g,
                                float eps, void* normed, int T, int S, int D, int dtype, cudaStream_t stream) {
     if (T == 0) return CVB_OK;
     if (T < 0 || S <= 0 || D <= 0) return CVB_E_SIZE;
     if (S > kMaxStreams) return CVB_E_UNSUPPORTED;
     if ((y != nullptr) != (mix != nullptr) || (y != nullptr) != (wout != nullptr)) return CVB_E_SHAPE;
-    if (y == nullptr && normed == nullptr) return CVB_E_SHAPE;
+    if ((y == nullptr && normed == nullptr) || (y2 != nullptr && y == nullptr)) return CVB_E_SHAPE;
     const size_t smem = (static_cast<size_t>(D) + 32) * sizeof(float);
     if (smem > 200 * 1024) return CVB_E_SIZE;
-    const bool wide = D % 4 == 0 && ((reinterpret_cast<uintptr_t>(X) | reinterpret_cast<uintptr_t>(y) | reinterpret_cast<uintptr_t>(normed)) & 15) == 0;
+    const bool wide = D % 4 == 0 && ((reinterpret_cast<uintptr_t>(X) | reinterpret_cast<uintptr_t>(y) | reinterpret_cast<uintptr_t>(y2) | reinterpret_cast<uintptr_t>(normed)) & 15) == 0;
 #define VEC(TY, NS)                                                                                                       \
     do {                                                                                                                  \
         if (smem > 48 * 1024)                                                                                             \
             cudaFuncSetAttribute(stream_step_vec_kernel<TY, NS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
-        launch_kernel(stream_step_vec_kernel<TY, NS>, dim3(T), dim3(kStreamThreads), smem, stream, X, (const TY*)y, mix, wout, win, g, \
+        launch_kernel(stream_step_vec_kernel<TY, NS>, dim3(T), dim3(kStreamThreads), smem, stream, X, (const TY*)y, (const TY*)y2, mix, wout, win, g, \
                       eps, (TY*)normed, D);                                                                               \
     } while (0)
 #define CALL(TY)                                                                                                          \
@@ -215,7 +217,7 @@ extern "C" int cvb_stream_step(float* X, const void* y, const float* mix, const 
         else if (wide && S == 3) { VEC(TY, 3); }                                                                          \
         else if (wide && S == 4) { VEC(TY, 4); }                                                                          \
         else                                                                                                              \
-        launch_kernel(stream_step_kernel<TY>, dim3(T), dim3(kStreamThreads), smem, stream, X, (const TY*)y, mix, wout, win, g, eps, \
+        launch_kernel(stream_step_kernel<TY>, dim3(T), dim3(kStreamThreads), smem, stream, X, (const TY*)y, (const TY*)y2, mix, wout, win, g, eps, \
                       (TY*)normed, S, D);                                                                                 \
     } while (0)
     CVB_DISPATCH_DTYPE(dtype, CALL);

@@ -961,29 +961,34 @@ def stream_embed(X: torch.Tensor, table: torch.Tensor, tokens: torch.Tensor, str
 
 def stream_step(X: torch.Tensor, streams: int, write=None, read=None, eps: float = 0.0, out: Optional[torch.Tensor] = None):
     """One pass over the streams X (float32 [T, streams * D], in place).  `write` = (y [T, D], mix float32 [S, S] (from, to),
-    b float32 [S]): x_t <- sum_s mix[s, t] x_s + b_t y.  `read` = (a float32 [S] or None for ones, g float32 with one element
+    b float32 [S]): x_t <- sum_s mix[s, t] x_s + b_t y; y may be a pair of tensors, which are added in float.  `read` = (a float32 [S] or None for ones, g float32 with one element
     or None for 1) with `out` [T, D]: out = T(u / sqrt(mean(u^2) + eps) * g), u = sum_s a_s x_s, of the streams after the write."""
     T = X.shape[0]
     S = int(streams)
     D = X.shape[1] // S
     y = mix = b = a = g = None
+    y2 = None
     if write is not None:
         y, mix, b = write
+        if isinstance(y, (tuple, list)):
+            y, y2 = (y[0], y[1]) if len(y) > 1 else (y[0], None)
     if read is not None:
         a, g = read
         if out is None:
             raise KernelError("stream_step: a read needs an output")
-    _cuda(X, y, mix, b, a, g, out); _contig(X, y, mix, b, a, g, out)
+    _cuda(X, y, y2, mix, b, a, g, out); _contig(X, y, y2, mix, b, a, g, out)
     act = out.dtype if out is not None else y.dtype
     if X.dtype != torch.float32 or X.shape[1] != S * D:
         raise KernelError("stream_step: the streams are float32 [T, S * D]")
+    if y2 is not None and (y2.shape != y.shape or y2.dtype != y.dtype):
+        raise KernelError("stream_step: the two addends of a write are alike")
     if y is not None and (y.shape != (T, D) or y.dtype != act or mix.dtype != torch.float32 or mix.numel() != S * S
                           or b.dtype != torch.float32 or b.numel() != S):
         raise KernelError("stream_step: write = (y [T, D], mix float32 [S, S], b float32 [S])")
     if out is not None and (out.shape != (T, D) or (a is not None and (a.dtype != torch.float32 or a.numel() != S))
                             or (g is not None and (g.dtype != torch.float32 or g.numel() != 1))):
         raise KernelError("stream_step: read = (a float32 [S], g float32 [1]) into out [T, D]")
-    _check(_hyper_lib().cvb_stream_step(_ptr(X), _ptr(y), _ptr(mix), _ptr(b), _ptr(a), _ptr(g), c_float(eps), _ptr(out), c_int(T),
+    _check(_hyper_lib().cvb_stream_step(_ptr(X), _ptr(y), _ptr(y2), _ptr(mix), _ptr(b), _ptr(a), _ptr(g), c_float(eps), _ptr(out), c_int(T),
                                         c_int(S), c_int(D), c_int(dtype_code(act)), _stream()), "stream_step")
     return out if out is not None else X
 

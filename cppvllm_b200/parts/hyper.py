@@ -28,8 +28,8 @@ from .base import Block, Norm, Part, WeightSpec, register_part
 
 @dataclass
 class StreamWrite:
-    """A sublayer's output that has not been written into the streams yet."""
-    y: torch.Tensor
+    """A sublayer's output (a tensor, or two that are to be added) that has not been written into the streams yet."""
+    y: object
     mix: torch.Tensor
     out: torch.Tensor
     streams: int
@@ -146,7 +146,9 @@ class HyperBlock(Block):
             a2, m2, b2 = self.w[self.ffn_name]
             x = ws.rows(self.ffn_norm.buffer, T, D, self.rt.dtype)
             ops.stream_step(X, S, write=(y, m1, b1), read=(a2, self.ffn_norm.weight), eps=self.ffn_norm.eps, out=x)
+            ctx.extras["takes_two_outputs"] = True      # a feed-forward may hand back (routed, shared): added in float by the write
             last = StreamWrite(self.ffn.forward(x, ctx), m2, b2, S)
+            ctx.extras.pop("takes_two_outputs", None)
         ahead = ctx.extras.get("norm_ahead")
         if ahead is not None and getattr(ahead, "first_of_hyper_block", False) and getattr(ahead, "streams", S) == S:
             return X, last                              # the next block's first kernel does the write

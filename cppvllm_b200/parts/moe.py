@@ -150,6 +150,8 @@ class RoutedGLU(FeedForward):
             gu = self._project(x, self.shared_gate_up, ws.rows("ffn_gate_up", T, 2 * self.shared_size, x.dtype), T)
             act = ops.swiglu(ws.rows("ffn_act", T, self.shared_size, x.dtype), gu)
             s = self._project(act, self.shared_down, ws.rows("ffn_shared", T, self.hidden_size, x.dtype), T)
+            if ctx.extras.get("takes_two_outputs"):      # the block adds the two in float when it writes them to its stream
+                return y, s
             ops.add_(y, s)
         return y
 

@@ -152,7 +152,8 @@ def test_streams_after_every_layer(rx_dirs, name, use_ref_kernels):
             h2, p2 = f(h, pending, ctx, cache, state)
             X = h2.double().view(ctx.num_tokens, S, -1)
             if p2 is not None:                         # the last write of the layer is still to come: apply it here
-                X = torch.einsum("sr,tsd->trd", p2.mix.double().view(S, S), X) + p2.out.double()[None, :, None] * p2.y.double()[:, None, :]
+                y = sum(part.double() for part in p2.y) if isinstance(p2.y, (tuple, list)) else p2.y.double()
+                X = torch.einsum("sr,tsd->trd", p2.mix.double().view(S, S), X) + p2.out.double()[None, :, None] * y[:, None, :]
             seen.append(X.sum(1).cpu())
             return h2, p2
         b.forward = wrapped
