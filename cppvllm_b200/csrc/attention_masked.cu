@@ -135,6 +135,120 @@ masked_qkv_prep_pairs_kernel(T* __restrict__ q_out, const T* __restrict__ packed
     }
 }
 
+// ---- 16 bytes per thread: head sizes whose chunk count is a power of two, a rotation in pairs (2i, 2i + 1) or none ------------
+//
+// One thread owns one 16-byte chunk of a head (8 bf16 or 4 float elements, whole pairs); the dk / N threads of a query or key
+// head are neighbours in a warp, so the sum of squares is a butterfly over the group.  The threads of a token are laid out as
+// all query and key chunks (padded to whole warps), then all value chunks.
+template <typename T> struct Chunk16;
+template <> struct Chunk16<float> {
+    static constexpr int N = 4;
+    static __device__ __forceinline__ void load(float (&v)[4], const float* p) { const float4 t = *reinterpret_cast<const float4*>(p); v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w; }
+    static __device__ __forceinline__ void store(float* p, const float (&v)[4]) { *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]); }
+};
+template <> struct Chunk16<__nv_bfloat16> {
+    static constexpr int N = 8;
+    static __device__ __forceinline__ void load(float (&v)[8], const __nv_bfloat16* p) {
+        const uint4 raw = *reinterpret_cast<const uint4*>(p);
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) { const float2 f = __bfloat1622float2(h[i]); v[2 * i] = f.x; v[2 * i + 1] = f.y; }
+    }
+    static __device__ __forceinline__ void store(__nv_bfloat16* p, const float (&v)[8]) {
+        uint4 raw;
+        __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&raw);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+        *reinterpret_cast<uint4*>(p) = raw;
+    }
+};
+
+template <typename T>
+__global__ void __launch_bounds__(128)
+masked_qkv_prep_vec_kernel(T* __restrict__ q_out, const T* __restrict__ packed, int stride, const float* __restrict__ q_w,
+                           const float* __restrict__ k_w, const float* __restrict__ cos_t, const float* __restrict__ sin_t,
+                           const int* __restrict__ positions, const int* __restrict__ slots, T* __restrict__ pages,
+                           T* __restrict__ vfirst_out, const T* __restrict__ vfirst_in, const float* __restrict__ lam_p,
+                           int H, int G, int dk, int dv, int rot, int planes, int page_size, int max_pos, float eps,
+                           int64_t total_slots, int qk_pad, int* __restrict__ err) {
+    pdl_trigger();
+    pdl_wait();
+    constexpr int N = Chunk16<T>::N;
+    const int chk = dk / N, chv = dv / N;
+    const int idx = blockIdx.y * 128 + threadIdx.x;
+    const int64_t t = blockIdx.x;
+    const T* row = packed + t * stride;
+    const int slot = slots != nullptr ? slots[t] : -1;
+    const int ew = dk + dv;
+    int64_t entry = -1;
+    if (slot >= 0 && pages != nullptr) {
+        if (slot >= total_slots) {
+            if ((threadIdx.x & 31) == 0) atomicExch(err, 2);
+        } else {
+            const int page = slot / page_size, off = slot - page * page_size;
+            entry = ((static_cast<int64_t>(page) * planes * G) * page_size + off) * ew;
+        }
+    }
+    float v[N];
+    if (idx >= qk_pad) {                                // a chunk of a value head
+        const int vi = idx - qk_pad;
+        if (vi >= G * chv) return;
+        const int g = vi / chv, e = (vi - g * chv) * N;
+        Chunk16<T>::load(v, row + H * dk + G * dk + g * dv + e);
+        if (vfirst_out != nullptr) Chunk16<T>::store(vfirst_out + t * G * dv + g * dv + e, v);
+        if (vfirst_in != nullptr) {
+            const float lam = lam_p[0];
+            float f[N];
+            Chunk16<T>::load(f, vfirst_in + t * G * dv + g * dv + e);
+#pragma unroll
+            for (int i = 0; i < N; ++i) v[i] = (1.f - lam) * v[i] + lam * f[i];
+        }
+        if (entry >= 0) Chunk16<T>::store(pages + entry + static_cast<int64_t>(g) * page_size * ew + dk + e, v);
+        return;
+    }
+    // a chunk of a query or key head; every lane of the warp walks the butterfly, live or not
+    const int task = min(idx / chk, H + G - 1), c = idx % chk;
+    const bool is_q = task < H;
+    const bool live = idx < (H + G) * chk && (is_q || entry >= 0);
+    const float* w = is_q ? q_w : k_w;
+    float ss = 0.f;
+    if (live) {
+        Chunk16<T>::load(v, row + task * dk + c * N);   // key heads lie behind the query heads in the row
+#pragma unroll
+        for (int i = 0; i < N; ++i) ss = fmaf(v[i], v[i], ss);
+    }
+    if (w != nullptr) {
+        for (int o = chk >> 1; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        const float inv = rsqrtf(ss / static_cast<float>(dk) + eps);
+        if (live) {
+#pragma unroll
+            for (int i = 0; i < N; ++i) v[i] = v[i] * inv * w[c * N + i];
+        }
+    }
+    if (!live) return;
+    const int half = rot >> 1;
+    if (cos_t != nullptr && c * N < rot) {
+        int pos = positions[t];
+        if (pos < 0 || pos >= max_pos) {
+            atomicExch(err, 3);
+            pos = pos < 0 ? 0 : max_pos - 1;
+        }
+        const float* c_row = cos_t + static_cast<int64_t>(pos) * half;
+        const float* s_row = sin_t + static_cast<int64_t>(pos) * half;
+#pragma unroll
+        for (int i = 0; i < N; i += 2) {
+            const int pr = (c * N + i) >> 1;
+            if (pr < half) {
+                const float cs = c_row[pr], sn = s_row[pr], x0 = v[i], x1 = v[i + 1];
+                v[i] = x0 * cs - x1 * sn;
+                v[i + 1] = x1 * cs + x0 * sn;
+            }
+        }
+    }
+    T* dst = is_q ? q_out + (t * H + task) * dk : pages + entry + static_cast<int64_t>(task - H) * page_size * ew;
+    Chunk16<T>::store(dst + c * N, v);
+}
+
 template <typename T>
 __global__ void __launch_bounds__(kPrepWarps * 32)
 masked_qkv_prep_kernel(T* __restrict__ q_out, const T* __restrict__ packed, int stride, const float* __restrict__ q_w,
@@ -940,8 +1054,20 @@ extern "C" int cvb_masked_qkv_prep(void* q_out, const void* packed, int T, int s
     const bool pairs = dk % 2 == 0 && dv % 2 == 0 && stride % 2 == 0 && dk <= 64 * kPrepPairs && (interleaved || !turns)
                        && ((reinterpret_cast<uintptr_t>(packed) | reinterpret_cast<uintptr_t>(q_out) | reinterpret_cast<uintptr_t>(pages)
                             | reinterpret_cast<uintptr_t>(vfirst_out) | reinterpret_cast<uintptr_t>(vfirst_in)) & 7) == 0;
+    // 16 bytes per thread where a head is a power of two of such chunks and everything is aligned to them
+    const int n16 = dtype == CVB_DTYPE_BF16 ? 8 : 4;
+    const int chk = dk / n16;
+    const bool vec16 = pairs && dk % n16 == 0 && dv % n16 == 0 && stride % n16 == 0 && chk <= 32 && (chk & (chk - 1)) == 0 && rot % 2 == 0
+                       && ((reinterpret_cast<uintptr_t>(packed) | reinterpret_cast<uintptr_t>(q_out) | reinterpret_cast<uintptr_t>(pages)
+                            | reinterpret_cast<uintptr_t>(vfirst_out) | reinterpret_cast<uintptr_t>(vfirst_in)) & 15) == 0;
+    const int qk_pad = vec16 ? ((H + G) * chk + 31) / 32 * 32 : 0;
+    const dim3 grid16(static_cast<unsigned>(T), vec16 ? static_cast<unsigned>((qk_pad + G * (dv / n16) + 127) / 128) : 1u);
 #define CALL(TY)                                                                                                          \
-    if (pairs)                                                                                                            \
+    if (vec16)                                                                                                            \
+    launch_kernel(masked_qkv_prep_vec_kernel<TY>, grid16, dim3(128), 0, stream, (TY*)q_out, (const TY*)packed, stride, q_w,           \
+                  k_w, cos_t, sin_t, positions, slots, (TY*)pages, (TY*)vfirst_out, (const TY*)vfirst_in, lam, H, G, dk, dv, rot,    \
+                  planes, page_size, max_pos, eps, total_slots, qk_pad, err_flag);                                        \
+    else if (pairs)                                                                                                       \
     launch_kernel(masked_qkv_prep_pairs_kernel<TY>, grid, dim3(kPrepWarps * 32), 0, stream, (TY*)q_out, (const TY*)packed, stride, q_w, \
                   k_w, cos_t, sin_t, positions, slots, (TY*)pages, (TY*)vfirst_out, (const TY*)vfirst_in, lam, H, G, dk, dv, rot,    \
                   planes, page_size, max_pos, eps, total_slots, err_flag);                                                \
