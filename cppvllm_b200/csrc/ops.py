@@ -1104,6 +1104,18 @@ def attn_masked_supported(dtype: torch.dtype, num_heads: int, num_kv_heads: int,
             and num_kv_heads > 0 and num_heads % num_kv_heads == 0 and num_heads // num_kv_heads <= 64)
 
 
+def attn_masked_decode_splits(num_seqs: int, num_kv_heads: int, visible_keys: int, sms: int = 148) -> int:
+    """Blocks per (request, kv head) of a decode step over entries of a key and its value: a block's warps keep two stages of
+    32 entries each, which at 128 + 128 elements fills an SM's shared memory, so the blocks of a step should be one wave: the
+    largest power of two (at most 8) that keeps them within the SMs and leaves every block four tiles or more."""
+    pairs = max(1, num_seqs * num_kv_heads)
+    tiles = max(1, (visible_keys + 31) // 32)
+    splits = 1
+    while splits < 8 and pairs * splits * 2 <= sms and tiles >= 4 * splits * 2:
+        splits *= 2
+    return splits
+
+
 def attn_masked_bf16(out: torch.Tensor, q: torch.Tensor, pages: torch.Tensor, block_tables: torch.Tensor, cu_seqlens: torch.Tensor,
                      positions: torch.Tensor, num_seqs: int, num_tiles: int, num_heads: int, num_kv_heads: int, dim: int, vdim: int,
                      page_size: int, scale: float, planes: int = 1, chunk: int = 0, window: int = 0, pool: int = 0,

@@ -748,7 +748,7 @@ def rumurax_kernel_pairs(s, pk):
     like = _us(lambda i: ops.attn_bias_bf16(att_b, q_b, e1_big[i % copies], tabs[i % copies], cu_b, pos_b, B, B, H, KV, hd, hd, page, scale,
                                             bias, all_single=True, splits=z, scratch=parts))
     like_bytes = B * ctx * KV * hd * 4.0
-    zm = ops.attn_keys_decode_splits(B, KV, RX_CHUNK)
+    zm = ops.attn_masked_decode_splits(B, KV, RX_CHUNK)
     new = _us(lambda i: ops.attn_masked_bf16(att_b, q_b, e1_big[i % copies], tabs[i % copies], cu_b, pos_b, B, B, H, KV, hd, hd, page, scale,
                                              chunk=RX_CHUNK, softcap=30.0, r1=r1, r2=r2, sink=sink, gate=gate_b, all_single=True, splits=zm,
                                              scratch=parts))

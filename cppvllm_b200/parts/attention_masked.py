@@ -139,7 +139,7 @@ class MaskedAttention(Mixer):
                     seen = min(seen, self.chunk)
                 if self.window:
                     seen = min(seen, self.window + (ctx.max_kv_len // self.pool if self.pool else 0))
-                splits = ops.attn_keys_decode_splits(ctx.num_seqs, G, seen)
+                splits = ops.attn_masked_decode_splits(ctx.num_seqs, G, seen)
                 if splits > 1:
                     most = ops.attn_keys_scratch_floats(self.rt.workspace.max_seqs, G, dv, 8)
                     scratch = self.rt.workspace.flat(f"attn_masked_parts_{G}_{dv}", most, torch.float32)
