@@ -498,7 +498,7 @@ struct MaskedAttnParams {
     int* err;
 };
 
-__device__ __forceinline__ float tanh_by_exp(float x) { return 1.f - 2.f / (1.f + __expf(2.f * x)); }
+__device__ __forceinline__ float tanh_by_exp(float x) { return 1.f - __fdividef(2.f, 1.f + __expf(2.f * x)); }
 
 template <int W, bool EXACT>
 __global__ void __launch_bounds__(kMThreads, W <= 64 ? 3 : 2)
@@ -807,6 +807,22 @@ attn_masked_decode_kernel(const MaskedAttnParams p) {
         int last_slot = -1, page = -1;
         const __nv_bfloat16* page_base = p.pages;
         int r = ld_r0, c = ld_c0;                         // chunk lane + 32 n is row (lane + 32 n) / CE: kept by increments
+        if (p.page_shift >= 5) {
+            // pages of 32 tokens and more (a power of two): the tile lies in ONE page, its rows side by side
+            const int slot = key0 >> p.page_shift;
+            page = slot < p.table_width ? table[slot] : -1;
+            const bool ok = page >= 0 && page < p.num_pages;
+            if (!ok) atomicExch(p.err, 4);
+            const __nv_bfloat16* base = ok ? p.pages + (((static_cast<int64_t>(page) * p.planes + plane) * p.G + kvh) * p.page_size
+                                                        + (key0 & (p.page_size - 1))) * E : p.pages;
+            const int live = ok ? hi - key0 : -1;         // rows 0..live hold entries the token may see
+            for (; r < kMDecKeys; r += ld_dr, c += ld_dc) {
+                if (c >= CE) { c -= CE; ++r; if (r >= kMDecKeys) break; }
+                const bool need = r <= live;
+                cp_async16(dst + r * LD + c * 8, need ? base + r * E + c * 8 : p.pages, need);
+            }
+            return;
+        }
         for (; r < kMDecKeys; r += ld_dr, c += ld_dc) {
             if (c >= CE) { c -= CE; ++r; if (r >= kMDecKeys) break; }
             const int j = key0 + r;

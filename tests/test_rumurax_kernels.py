@@ -295,13 +295,14 @@ def test_gate_per_element(dtype):
 
 
 @pytest.mark.parametrize("splits", [1, 2, 4])
+@pytest.mark.parametrize("page", [16, 32])
 @pytest.mark.parametrize("kind", ["chunked", "windowed", "causal"])
-def test_decoded_tokens_of_several_requests(kind, splits):
+def test_decoded_tokens_of_several_requests(kind, page, splits):
     """The form for steps of one token per request (tiles shared out among warps and blocks, parts merged, the sink and the gate
     joined once at the merge) against the general kernel, over requests of unequal lengths in shuffled pages."""
     from cppvllm_b200.csrc import ops
     g = torch.Generator().manual_seed(11)
-    H, G, dk, dv, page = 8, 2, 48, 64, 16
+    H, G, dk, dv = 8, 2, 48, 64                     # pages of 32 tokens hold a tile of the decode form whole: one page lookup per tile
     chunk, window, pool, cap = (64, 0, 0, 20.0) if kind == "chunked" else ((0, 136, 12, 0.0) if kind == "windowed" else (0, 0, 0, 0.0))
     planes = 2 if pool else 1
     lens = [1, 17, 64, 65, 300, 777, 128, 137]
