@@ -11,7 +11,7 @@
     rx_c    96   150     2     windowed 6/2 heads, 64 (32 turned)/64, window 40, blocks of 8, mixing; 4 experts, 2 per token, 32 wide, shared 32
                                chunked 4/2 heads, 32/64, chunks of 48, cap 12, mixing; 4 experts, 1 per token
                                latent 4 heads, 32 + 16 (16 turned), values 32, latent 64; none
-                               windowed 4/2 heads, 48 (48 turned)/64, window 70, blocks of 16, mixing; 2 experts, 1 per token
+                               windowed 4/2 heads, 80 (80 turned)/64, window 70, blocks of 16, mixing; 2 experts, 1 per token
                                chunked 2/1 heads, 64/64, chunks of 100, cap 30, no mixing; 3 experts, 3 per token, shared 16
     rx_d    50    61  (none)   chunked 5/5 heads, 10/6, chunks of 5, cap 2; 6 experts, 3 per token, 12 wide, shared 12
                                windowed 1/1 head, 6 (4 turned)/3, window 3, blocks of 2; none
@@ -73,7 +73,7 @@ RX_C = {"architecture": "Rumurax", "vocab": 150, "width": 96, "streams": 2, "nor
         "layers": [_layer(_windowed(6, 2, 64, 64, 40, 8, 32, 10000.0, 0.125), _moe(4, 2, 32, shared=32)),
                    _layer(_chunked(4, 2, 32, 64, 48, 12.0, 0.18), _moe(4, 1, 32)),
                    _layer(_latent(4, 32, 16, 32, 64, 16, 500000.0, 0.15), None),
-                   _layer(_windowed(4, 2, 48, 64, 70, 16, 48, 300.0, 0.14), _moe(2, 1, 64)),
+                   _layer(_windowed(4, 2, 80, 64, 70, 16, 80, 300.0, 0.11), _moe(2, 1, 64)),
                    _layer(_chunked(2, 1, 64, 64, 100, 30.0, 0.125, v_mix=False), _moe(3, 3, 16, shared=16))]}
 RX_D = {"architecture": "Rumurax", "vocab": 61, "width": 50, "norm": {"eps": 1e-4},
         "layers": [_layer(_chunked(5, 5, 10, 6, 5, 2.0, 0.4, v_mix=False), _moe(6, 3, 12, shared=12)),

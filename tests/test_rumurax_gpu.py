@@ -209,3 +209,26 @@ def test_trace_replay_command_line(rx_dirs, tmp_path):
     portions(tb, "r", toks, sizes=(2, 5, 2, 31))
     out = run_trace(d, "float32", tb.steps, 128, str(tmp_path / "o"), ["--block-size", "64"])
     check(rows_by_position(tb.steps, out), {"r": rm.reference(d, toks).float()}, "float32")
+
+
+def test_the_example_command_line(rx_dirs):
+    """`example <model_dir>`: the registry picks the design by config.json, the pool is sized from what the device has left
+    after the weights, and every generated token is the plain implementation's best one."""
+    import ast
+    import os
+    import subprocess
+    import sys
+    d = rx_dirs["rx_a"]
+    prompt = rm.clear_tokens(d, 9, 77)
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    r = subprocess.run([sys.executable, os.path.join(root, "bin", "example"), d, "--dtype", "float32", "--prompt", ",".join(map(str, prompt)),
+                        "--temperature", "0", "--max-tokens", "5", "--ignore-eos", "--max-num-seqs", "4", "--max-model-len", "64",
+                        "--max-num-batched-tokens", "64", "--block-size", "16"], capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stderr[-2000:]
+    line = [l for l in r.stdout.splitlines() if l.startswith("Completion:")][0]
+    got = ast.literal_eval(line[len("Completion:"):].strip())
+    assert len(got) == 5
+    ref = rm.reference(d, (prompt + got)[:-1])
+    for i, tok in enumerate(got):
+        row = ref[len(prompt) - 1 + i]
+        assert row[tok] >= row.max() - 1e-4 * max(1.0, float(row.abs().max()))

@@ -23,7 +23,7 @@ def dev():
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("S,D", [(1, 64), (2, 50), (3, 320), (4, 96), (8, 40)])
+@pytest.mark.parametrize("S,D", [(1, 64), (2, 50), (3, 352), (4, 96), (8, 40)])
 def test_stream_step(dtype, S, D):
     from cppvllm_b200.csrc import ops
     g = torch.Generator().manual_seed(S * 100 + D)
@@ -120,7 +120,7 @@ CASES = [
     # name, H, G, dk, dv, chunk, window, pool, cap, bias, sink, gate, rot, page, L
     ("chunked", 4, 2, 16, 32, 24, 0, 0, 30.0, True, True, True, 0, 16, 150),
     ("chunk_is_page", 2, 1, 32, 32, 32, 0, 0, 0.0, True, False, False, 0, 32, 100),
-    ("windowed_blocks", 4, 2, 48, 64, 0, 40, 8, 0.0, False, False, False, 16, 16, 200),
+    ("windowed_blocks", 4, 2, 32, 48, 0, 40, 8, 0.0, False, False, False, 16, 16, 200),
     ("window_of_one", 2, 2, 16, 16, 0, 1, 1, 0.0, False, False, False, 16, 16, 70),
     ("blocks_wider_than_pages", 8, 2, 64, 64, 0, 20, 24, 0.0, False, True, False, 32, 16, 300),
     ("plain_causal", 3, 1, 128, 128, 0, 0, 0, 0.0, False, False, True, 0, 64, 130),
@@ -245,7 +245,7 @@ def test_value_mixing_and_kept_values(dtype):
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("T,D,E,top,I,shared,kernel", [(1, 64, 4, 2, 32, 16, ""), (9, 50, 5, 5, 12, 0, "rows"), (70, 128, 8, 3, 64, 32, "tcgen05"),
-                                                        (300, 320, 8, 1, 64, 128, ""), (5, 96, 1, 1, 24, 8, "")])
+                                                        (300, 256, 6, 2, 48, 96, ""), (5, 96, 1, 1, 24, 8, "")])
 def test_logistic_router_and_experts_that_weigh_their_input(dtype, T, D, E, top, I, shared, kernel):
     from cppvllm_b200.csrc import ops
     dt = DT[dtype]
@@ -302,8 +302,8 @@ def test_decoded_tokens_of_several_requests(kind, page, splits):
     joined once at the merge) against the general kernel, over requests of unequal lengths in shuffled pages."""
     from cppvllm_b200.csrc import ops
     g = torch.Generator().manual_seed(11)
-    H, G, dk, dv = 8, 2, 48, 64                     # pages of 32 tokens hold a tile of the decode form whole: one page lookup per tile
-    chunk, window, pool, cap = (64, 0, 0, 20.0) if kind == "chunked" else ((0, 136, 12, 0.0) if kind == "windowed" else (0, 0, 0, 0.0))
+    H, G, dk, dv = 6, 3, 32, 48                     # pages of 32 tokens hold a tile of the decode form whole: one page lookup per tile
+    chunk, window, pool, cap = (80, 0, 0, 15.0) if kind == "chunked" else ((0, 100, 10, 0.0) if kind == "windowed" else (0, 0, 0, 0.0))
     planes = 2 if pool else 1
     lens = [1, 17, 64, 65, 300, 777, 128, 137]
     B, E = len(lens), dk + dv
