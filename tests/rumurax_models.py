@@ -13,12 +13,17 @@
                                latent 4 heads, 32 + 16 (16 turned), values 32, latent 64; none
                                windowed 4/2 heads, 80 (80 turned)/64, window 70, blocks of 16, mixing; 2 experts, 1 per token
                                chunked 2/1 heads, 64/64, chunks of 100, cap 30, no mixing; 3 experts, 3 per token, shared 16
+    rx_e    64    83     6     windowed 32/1 heads, 16 (16 turned)/16, window 30, blocks of 5; 3 experts, 2 per token, 16 wide, shared 8
+                               chunked 2/1 heads, 160/144, chunks of 40, cap 8; none
+                               latent 2 heads, 24 + 8 (8 turned), values 40, latent 200; 9 experts, 1 per token, 8 wide
     rx_d    50    61  (none)   chunked 5/5 heads, 10/6, chunks of 5, cap 2; 6 experts, 3 per token, 12 wide, shared 12
                                windowed 1/1 head, 6 (4 turned)/3, window 3, blocks of 2; none
 Widths of 50 and rows of 10, 6 or 3 elements fit no vector width; rx_b has one stream with learned weights, rx_d none at all
 (no 'streams' key: a plain residual sum); rx_b starts with a chunked layer and has a window without blocks; rx_c has the
 sizes the tensor-core kernels take, keys and values of different sizes and a layer that mixes no values among layers that do;
-in rx_d windows and chunks are a handful of tokens.  Scales, eps, caps and bases all differ."""
+in rx_d windows and chunks are a handful of tokens; rx_e has six streams (beyond the stream kernel's vector forms), 32 query heads
+on one kv head (beyond the 16 rows of the form for decoded tokens), heads of 160 and 144 elements and a latent of 200 (beyond
+what the tensor-core kernels take, in bfloat16 too).  Scales, eps, caps and bases all differ."""
 import json
 import os
 
@@ -79,8 +84,13 @@ RX_D = {"architecture": "Rumurax", "vocab": 61, "width": 50, "norm": {"eps": 1e-
         "layers": [_layer(_chunked(5, 5, 10, 6, 5, 2.0, 0.4, v_mix=False), _moe(6, 3, 12, shared=12)),
                    _layer(_windowed(1, 1, 6, 3, 3, 2, 4, 20.0, 0.5, v_mix=False), None)]}
 
+RX_E = {"architecture": "Rumurax", "vocab": 83, "width": 64, "streams": 6, "norm": {"eps": 1e-5},
+        "layers": [_layer(_windowed(32, 1, 16, 16, 30, 5, 16, 5000.0, 0.25, v_mix=False), _moe(3, 2, 16, shared=8)),
+                   _layer(_chunked(2, 1, 160, 144, 40, 8.0, 0.08, v_mix=False), None),
+                   _layer(_latent(2, 24, 8, 40, 200, 8, 1000.0, 0.18), _moe(9, 1, 8))]}
+
 # name -> (config, seed, page size)
-SETUPS = {"rx_a": (RX_A, 31, 16), "rx_b": (RX_B, 32, 32), "rx_c": (RX_C, 33, 16), "rx_d": (RX_D, 34, 64)}
+SETUPS = {"rx_a": (RX_A, 31, 16), "rx_b": (RX_B, 32, 32), "rx_c": (RX_C, 33, 16), "rx_d": (RX_D, 34, 64), "rx_e": (RX_E, 35, 32)}
 
 
 def write_model(path, cfg, seed, sharpen=4.0):

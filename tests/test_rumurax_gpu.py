@@ -13,7 +13,7 @@ from trace_util import TraceBuilder, needed_max_tokens, portions, rows_by_positi
 pytestmark = pytest.mark.gpu
 
 TOL = {"float32": 3e-5, "bfloat16": 5e-2}        # of the largest logit; a fault of a mechanism moves logits by tenths of it
-NAMES = ["rx_a", "rx_b", "rx_c", "rx_d"]
+NAMES = ["rx_a", "rx_b", "rx_c", "rx_d", "rx_e"]
 
 
 @pytest.fixture(scope="module")
