@@ -340,32 +340,34 @@ pool_entries_kernel(T* __restrict__ pages, const int* __restrict__ block_tables,
     const int* table = block_tables + static_cast<int64_t>(seq_of_token[t]) * table_width;
     const int dst_page = b / page_size < table_width ? table[b / page_size] : -1;
     if (dst_page < 0 || dst_page >= num_pages) { if (threadIdx.x == 0) atomicExch(err, 4); return; }
-    float sum[4] = {0.f, 0.f, 0.f, 0.f};               // entries of up to 512 elements: four per thread
-    for (int j0 = p - pool + 1; j0 <= p; j0 += 128) {
-        const int n = min(128, p - j0 + 1);
-        __syncthreads();
-        if (threadIdx.x < n) {
-            const int j = j0 + threadIdx.x;
-            const int page = j / page_size < table_width ? table[j / page_size] : -1;
-            if (page < 0 || page >= num_pages) { atomicExch(err, 4); off[threadIdx.x] = -1; }
-            else off[threadIdx.x] = (((static_cast<int64_t>(page) * 2 + 0) * G + g) * page_size + j % page_size) * ew;
+    const int64_t dst = (((static_cast<int64_t>(dst_page) * 2 + 1) * G + g) * page_size + b % page_size) * ew;
+    for (int e0 = 0; e0 < ew; e0 += 512) {              // 512 elements of the entry at a time: four per thread
+        float sum[4] = {0.f, 0.f, 0.f, 0.f};
+        for (int j0 = p - pool + 1; j0 <= p; j0 += 128) {
+            const int n = min(128, p - j0 + 1);
+            __syncthreads();
+            if (threadIdx.x < n) {
+                const int j = j0 + threadIdx.x;
+                const int page = j / page_size < table_width ? table[j / page_size] : -1;
+                if (page < 0 || page >= num_pages) { atomicExch(err, 4); off[threadIdx.x] = -1; }
+                else off[threadIdx.x] = (((static_cast<int64_t>(page) * 2 + 0) * G + g) * page_size + j % page_size) * ew;
+            }
+            __syncthreads();
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const int e = e0 + threadIdx.x + k * 128;
+                if (e >= ew) break;
+                float acc = sum[k];
+#pragma unroll 8
+                for (int i = 0; i < n; ++i) acc += off[i] >= 0 ? to_float(pages[off[i] + e]) : 0.f;     // rising positions, one sum
+                sum[k] = acc;
+            }
         }
-        __syncthreads();
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
-            const int e = threadIdx.x + k * 128;
-            if (e >= ew) break;
-            float acc = sum[k];
-#pragma unroll 8
-            for (int i = 0; i < n; ++i) acc += off[i] >= 0 ? to_float(pages[off[i] + e]) : 0.f;     // rising positions, one sum
-            sum[k] = acc;
+            const int e = e0 + threadIdx.x + k * 128;
+            if (e < ew) pages[dst + e] = from_float<T>(sum[k] / static_cast<float>(pool));
         }
-    }
-    const int64_t dst = (((static_cast<int64_t>(dst_page) * 2 + 1) * G + g) * page_size + b % page_size) * ew;
-#pragma unroll
-    for (int k = 0; k < 4; ++k) {
-        const int e = threadIdx.x + k * 128;
-        if (e < ew) pages[dst + e] = from_float<T>(sum[k] / static_cast<float>(pool));
     }
 }
 
@@ -1100,7 +1102,7 @@ extern "C" int cvb_pool_entries(void* pages, const int* block_tables, int table_
                                 int T, int G, int ew, int pool, int page_size, int num_pages, int dtype, int* err_flag,
                                 cudaStream_t stream) {
     if (T == 0) return CVB_OK;
-    if (T < 0 || G <= 0 || ew <= 0 || ew > 512 || pool <= 0 || page_size <= 0 || table_width <= 0 || num_pages <= 0 || G > 65535) return CVB_E_SIZE;
+    if (T < 0 || G <= 0 || ew <= 0 || pool <= 0 || page_size <= 0 || table_width <= 0 || num_pages <= 0 || G > 65535) return CVB_E_SIZE;
 #define CALL(TY)                                                                                                          \
     launch_kernel(pool_entries_kernel<TY>, dim3(T, G), dim3(128), 0, stream, (TY*)pages, block_tables, table_width, seq_of_token,   \
                   positions, G, ew, pool, page_size, num_pages, err_flag)

@@ -126,6 +126,7 @@ CASES = [
     ("plain_causal", 3, 1, 128, 128, 0, 0, 0, 0.0, False, False, True, 0, 64, 130),
     ("odd_sizes", 5, 5, 10, 6, 7, 0, 0, 4.0, True, True, True, 0, 16, 60),
     ("odd_windowed", 3, 1, 6, 3, 0, 5, 3, 0.0, False, False, False, 4, 32, 75),
+    ("wide_entries_long_blocks", 2, 1, 320, 256, 0, 10, 150, 0.0, False, False, False, 8, 32, 400),
 ]
 
 
